@@ -1,0 +1,780 @@
+// Head-sparse attention block for decode: QKV projection of selected heads (with lazy K/V back-fill),
+// single-query attention over the fp16 caches for those heads, head-gathered output projection, and
+// the device-resident lazy-K/V state machine.
+//
+// Cache layouts (one layer, as the reference keeps them for its decode kernel,
+// Dejavu/src/ops/triton/attention_proj_sparse.py:540-546, 410-416):
+//   K cache (B, nheads, hd/8, S, 8)   element (h, j, pos) at ((h*(hd/8) + j/8)*S + pos)*8 + j%8
+//   V cache (B, nheads, S, hd)        element (h, pos, j) at (h*S + pos)*hd + j
+//
+// Algorithmic bytes: QKV 3*a*hd*d*2 (+bias, x); attention 2*a*len*hd*2; out_proj d*a*hd*2 (+bias, ctx, y).
+#include "common.cuh"
+
+namespace djv {
+
+// ------------------------------------------------------------------------------------------
+// state words, see DJV_ATTN_STATE_* in the header
+// ------------------------------------------------------------------------------------------
+enum { ST_SLOT = 0, ST_BASE = 1, ST_NEFF = 2, ST_STATUS = 3 };
+__device__ __forceinline__ int *st_pending(int *st) { return st + DJV_ATTN_STATE_HDR; }
+__device__ __forceinline__ int *st_eff(int *st, int nheads) { return st + DJV_ATTN_STATE_HDR + nheads; }
+__device__ __forceinline__ int *st_rowmask(int *st, int nheads) {
+  return st + DJV_ATTN_STATE_HDR + 2 * nheads;
+}
+
+__global__ void attn_state_reset_kernel(int *st, int nheads, int prompt_len) {
+  const int words = DJV_ATTN_STATE_WORDS(nheads);
+  for (int i = threadIdx.x; i < words; i += blockDim.x) st[i] = 0;
+  __syncthreads();
+  if (threadIdx.x == 0) st[ST_BASE] = prompt_len;
+}
+
+// Step 1 of djv_attn_step: stash x in the window, pick the heads in use, update `pending`.
+__global__ void __launch_bounds__(1024)
+attn_prep_kernel(int *__restrict__ st, const int *__restrict__ head_idx, int nnz,
+                 const __half *__restrict__ x, __half *__restrict__ x_ring, int d, int nheads, int S) {
+  const int tid = threadIdx.x;
+  const int slot = st[ST_SLOT], base = st[ST_BASE];
+  int *pending = st_pending(st), *eff = st_eff(st, nheads), *rowmask = st_rowmask(st, nheads);
+  const bool bad = slot < 0 || slot >= DJV_KV_WINDOW || base < 0 || base + slot >= S;
+  if (bad) {
+    if (tid == 0) {
+      st[ST_STATUS] = DJV_ERR_INVALID;
+      st[ST_NEFF] = 0;
+    }
+    return;
+  }
+  // x_ring[slot] = x
+  const uint4 *src = reinterpret_cast<const uint4 *>(x);
+  uint4 *dst = reinterpret_cast<uint4 *>(x_ring + (size_t)slot * d);
+  for (int c = tid; c < d / 8; c += blockDim.x) dst[c] = src[c];
+
+  const bool all = (head_idx == nullptr) || (slot == DJV_KV_WINDOW - 1);
+  const int bit = 1 << slot;
+  __shared__ int selected[1024];
+  __shared__ int warp_tot[32];
+  for (int h = tid; h < nheads; h += blockDim.x) selected[h] = all ? 1 : 0;
+  __syncthreads();
+  if (!all)
+    for (int i = tid; i < nnz; i += blockDim.x) {
+      const int h = head_idx[i];
+      if (h >= 0 && h < nheads) selected[h] = 1;  // duplicates collapse here
+    }
+  __syncthreads();
+  // heads in use are emitted in ascending head order: exclusive scan of the flags (nheads <= 1024)
+  const int lane = tid % WARP, warp = tid / WARP;
+  const int flag = (tid < nheads) ? selected[tid] : 0;
+  const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+  const int in_warp = __popc(ballot & ((1u << lane) - 1u));
+  if (lane == 0) warp_tot[warp] = __popc(ballot);
+  __syncthreads();
+  int before = 0, total = 0;
+  for (int w2 = 0; w2 < 32; ++w2) {
+    const int t = warp_tot[w2];
+    if (w2 < warp) before += t;
+    total += t;
+  }
+  if (tid < nheads) {
+    if (flag) {
+      const int pos = before + in_warp;
+      eff[pos] = tid;
+      rowmask[pos] = pending[tid] | bit;
+      pending[tid] = 0;
+    } else {
+      pending[tid] |= bit;
+    }
+  }
+  if (tid == 0) st[ST_NEFF] = total;
+}
+
+__global__ void attn_finish_kernel(int *st) {
+  if (threadIdx.x == 0 && st[ST_STATUS] == 0) {
+    int slot = st[ST_SLOT] + 1;
+    if (slot >= DJV_KV_WINDOW) {
+      slot = 0;
+      st[ST_BASE] += DJV_KV_WINDOW;
+    }
+    st[ST_SLOT] = slot;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// QKV projection of selected heads for up to 16 token rows.
+// A block owns QKV_RPB consecutive output rows j of one (head, q|k|v) pair, so every warp group in
+// the block sees the same set of token rows and the block-wide barriers are uniform.
+//   MODE 0: operator semantics (rows = batch_idx[i,:] >= 0, output y (T,3,nheads,hd))
+//   MODE 1: decode step (rows = bits of rowmask[i]; q of the current slot -> q_out, K/V -> caches)
+// ------------------------------------------------------------------------------------------
+constexpr int QKV_THREADS = 256;
+constexpr int QKV_WARPS = QKV_THREADS / WARP;
+constexpr int QKV_RPB = 8;
+
+struct QkvArgs {
+  const __half *w;     // (3,nheads,hd,d)
+  const __half *bias;  // (3,nheads,hd) or null
+  const __half *x;     // (T,d) or x_ring (16,d)
+  int d, nheads, hd, nnz, T;
+  // MODE 0
+  __half *y;
+  const int *head_idx;
+  const int *batch_idx;
+  // MODE 1
+  int *state;
+  __half *q_out, *k_cache, *v_cache;
+  int S;
+};
+
+template <int NB, int WPR>
+__device__ __forceinline__ void multi_rowdot(const uint4 *wp, const uint4 *(&xp)[NB], int nchunks,
+                                             int glane, float (&acc)[NB]) {
+  constexpr int GLANES = WARP * WPR;
+  constexpr int U = 4;
+#pragma unroll
+  for (int r = 0; r < NB; ++r) acc[r] = 0.f;
+  for (int c0 = glane; c0 < nchunks; c0 += GLANES * U) {
+    uint4 wv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = c0 + u * GLANES;
+      wv[u] = (c < nchunks) ? ld_stream16(wp + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = c0 + u * GLANES;
+      if (c < nchunks) {
+#pragma unroll
+        for (int r = 0; r < NB; ++r) acc[r] = dot8(wv[u], ld_cached16(xp[r] + c), acc[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < NB; ++r) acc[r] = warp_sum(acc[r]);
+}
+
+template <int MODE, int WPR>
+__global__ void __launch_bounds__(QKV_THREADS) qkv_sparse_kernel(QkvArgs a) {
+  constexpr int GROUPS = QKV_WARPS / WPR;
+  __shared__ float red[QKV_WARPS][DJV_KV_WINDOW];
+  __shared__ int rows_s[DJV_KV_WINDOW];
+  __shared__ int nrows_s;
+
+  const int jblocks = a.hd / QKV_RPB;
+  const int pair = blockIdx.x / jblocks;  // i*3 + qkv
+  const int jb = blockIdx.x % jblocks;
+  const int i = pair / 3, qkv = pair % 3;
+
+  int n_eff, slot = 0, base = 0;
+  if (MODE == 0) {
+    n_eff = a.nnz;
+  } else {
+    n_eff = a.state[ST_NEFF];
+    slot = a.state[ST_SLOT];
+    base = a.state[ST_BASE];
+  }
+  if (i >= n_eff) return;
+  const int h = (MODE == 0) ? a.head_idx[i] : st_eff(a.state, a.nheads)[i];
+
+  // the token rows this (head, q|k|v) pair computes
+  if (threadIdx.x == 0) {
+    int n = 0;
+    if (MODE == 0) {
+      for (int t = 0; t < a.T; ++t) {
+        const int r = a.batch_idx[i * a.T + t];
+        if (r >= 0) rows_s[n++] = r;
+      }
+    } else {
+      if (qkv == 0) {
+        rows_s[n++] = slot;
+      } else {
+        const unsigned m = (unsigned)st_rowmask(a.state, a.nheads)[i];
+        for (int s = 0; s <= slot; ++s)
+          if (m >> s & 1u) rows_s[n++] = s;
+      }
+    }
+    nrows_s = n;
+  }
+  __syncthreads();
+  const int nrows = nrows_s;
+  if (nrows == 0) return;
+
+  const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
+  const int group = warp / WPR, wig = warp % WPR, glane = wig * WARP + lane;
+  const int nchunks = a.d / 8;
+  const uint4 *Xv = reinterpret_cast<const uint4 *>(a.x);
+
+  for (int jj = group; jj < QKV_RPB; jj += GROUPS) {
+    const int j = jb * QKV_RPB + jj;
+    const size_t wrow = ((size_t)qkv * a.nheads + h) * a.hd + j;
+    const uint4 *wp = reinterpret_cast<const uint4 *>(a.w + wrow * a.d);
+    const float bv = a.bias ? __half2float(a.bias[wrow]) : 0.f;
+
+    for (int r0 = 0; r0 < nrows; r0 += 4) {
+      const int nb = min(4, nrows - r0);
+      float acc[4];
+      const uint4 *xp[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) xp[r] = Xv + (size_t)rows_s[r0 + (r < nb ? r : 0)] * nchunks;
+      if (nb == 1) {
+        const uint4 *x1[1] = {xp[0]};
+        float a1[1];
+        multi_rowdot<1, WPR>(wp, x1, nchunks, glane, a1);
+        acc[0] = a1[0];
+      } else if (nb == 2) {
+        const uint4 *x2[2] = {xp[0], xp[1]};
+        float a2[2];
+        multi_rowdot<2, WPR>(wp, x2, nchunks, glane, a2);
+        acc[0] = a2[0];
+        acc[1] = a2[1];
+      } else {
+        multi_rowdot<4, WPR>(wp, xp, nchunks, glane, acc);
+      }
+      if (WPR > 1) {
+        if (lane == 0) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) red[warp][r] = acc[r];
+        }
+        // all groups run the same (jj, r0) trip counts, so this barrier is block-uniform
+        __syncthreads();
+        if (wig == 0 && lane == 0) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            float s = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < WPR; ++w2) s += red[group * WPR + w2][r];
+            acc[r] = s;
+          }
+        }
+      }
+      if (wig == 0 && lane == 0) {
+        for (int r = 0; r < nb; ++r) {
+          const __half out = __float2half_rn(acc[r] + bv);
+          const int row = rows_s[r0 + r];
+          if (MODE == 0) {
+            a.y[(((size_t)row * 3 + qkv) * a.nheads + h) * a.hd + j] = out;
+          } else if (qkv == 0) {
+            a.q_out[(size_t)h * a.hd + j] = out;
+          } else if (qkv == 1) {
+            const int pos = base + row;
+            a.k_cache[(((size_t)h * (a.hd / 8) + j / 8) * a.S + pos) * 8 + j % 8] = out;
+          } else {
+            const int pos = base + row;
+            a.v_cache[((size_t)h * a.S + pos) * a.hd + j] = out;
+          }
+        }
+      }
+      if (WPR > 1) __syncthreads();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Single-query attention for a list of heads, split over the cached tokens.
+// grid = (head slots, batch, splits); 128 threads. Partial (max, sum, out[hd]) per split goes to
+// scratch; the last split to finish for a (head, batch) combines them and writes fp16 context.
+// scratch layout: [counters: 4096 B][partials: slots*B*splits*(hd+2) floats]
+// ------------------------------------------------------------------------------------------
+constexpr int AT_THREADS = 128;
+constexpr int AT_MAX_SPLIT_TOKENS = 512;  // tokens one block handles at most per pass
+constexpr int AT_COUNTER_BYTES = 4096;
+
+struct AttnArgs {
+  __half *ctx;           // (B,nheads,hd)
+  const __half *q;       // (B,nheads,hd)
+  const __half *k_cache, *v_cache;
+  const int *head_idx;   // explicit list or null (= identity)
+  const int *state;      // when non-null: heads/n_eff/len come from the lazy-KV state
+  int nnz, nheads, hd, S, len;
+  float scale;
+  float *partial;
+  unsigned *counters;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
+  constexpr int CH = HD / 8;           // 16-byte chunks per head row
+  constexpr int RPI = AT_THREADS / CH; // V rows per iteration
+  __shared__ float qs[HD];
+  __shared__ float sc[AT_MAX_SPLIT_TOKENS];
+  __shared__ float redf[AT_THREADS / WARP];
+  __shared__ float osum[RPI][HD];
+  __shared__ int is_last;
+
+  const int tid = threadIdx.x, lane = tid % WARP, warp = tid / WARP;
+  const int i = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
+  int n_eff = a.nnz, len = a.len;
+  if (a.state) {
+    n_eff = a.state[ST_NEFF];
+    len = a.state[ST_BASE] + a.state[ST_SLOT] + 1;
+  }
+  if (i >= n_eff) return;
+  int h;
+  if (a.state)
+    h = a.state[DJV_ATTN_STATE_HDR + a.nheads + i];
+  else
+    h = a.head_idx ? a.head_idx[i] : i;
+
+  const size_t bh = (size_t)b * a.nheads + h;
+  const __half *Kh = a.k_cache + bh * (size_t)a.S * HD;
+  const __half *Vh = a.v_cache + bh * (size_t)a.S * HD;
+  for (int j = tid; j < HD; j += AT_THREADS) qs[j] = __half2float(a.q[bh * HD + j]) * a.scale;
+  __syncthreads();
+
+  const int chunk = (len + nsplit - 1) / nsplit;
+  const int t_begin = min(len, sp * chunk), t_end = min(len, t_begin + chunk);
+
+  float m_run = -INFINITY, l_run = 0.f;
+  float oacc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) oacc[e] = 0.f;
+  const int vrow = tid / CH, vch = tid % CH;
+
+  for (int p0 = t_begin; p0 < t_end; p0 += AT_MAX_SPLIT_TOKENS) {
+    const int pn = min(AT_MAX_SPLIT_TOKENS, t_end - p0);
+    // scores: one thread per token
+    float lmax = -INFINITY;
+    for (int t = tid; t < pn; t += AT_THREADS) {
+      const int pos = p0 + t;
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const uint4 kv = ld_stream16(Kh + ((size_t)c * a.S + pos) * 8);
+        const float2 k0 = h2f(kv.x), k1 = h2f(kv.y), k2 = h2f(kv.z), k3 = h2f(kv.w);
+        s = fmaf(qs[c * 8 + 0], k0.x, s);
+        s = fmaf(qs[c * 8 + 1], k0.y, s);
+        s = fmaf(qs[c * 8 + 2], k1.x, s);
+        s = fmaf(qs[c * 8 + 3], k1.y, s);
+        s = fmaf(qs[c * 8 + 4], k2.x, s);
+        s = fmaf(qs[c * 8 + 5], k2.y, s);
+        s = fmaf(qs[c * 8 + 6], k3.x, s);
+        s = fmaf(qs[c * 8 + 7], k3.y, s);
+      }
+      sc[t] = s;
+      lmax = fmaxf(lmax, s);
+    }
+    lmax = warp_max(lmax);
+    if (lane == 0) redf[warp] = lmax;
+    __syncthreads();
+    float m_new = m_run;
+#pragma unroll
+    for (int w2 = 0; w2 < AT_THREADS / WARP; ++w2) m_new = fmaxf(m_new, redf[w2]);
+    __syncthreads();
+    float lsum = 0.f;
+    for (int t = tid; t < pn; t += AT_THREADS) {
+      const float p = __expf(sc[t] - m_new);
+      sc[t] = p;
+      lsum += p;
+    }
+    lsum = warp_sum(lsum);
+    if (lane == 0) redf[warp] = lsum;
+    __syncthreads();
+    float ltot = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < AT_THREADS / WARP; ++w2) ltot += redf[w2];
+    const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
+    l_run = l_run * corr + ltot;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) oacc[e] *= corr;
+    m_run = m_new;
+    // P.V: CH lanes cover one V row, RPI rows per iteration
+    for (int t = vrow; t < pn; t += RPI) {
+      const uint4 vv = ld_stream16(Vh + (size_t)(p0 + t) * HD + vch * 8);
+      const float p = sc[t];
+      const float2 v0 = h2f(vv.x), v1 = h2f(vv.y), v2 = h2f(vv.z), v3 = h2f(vv.w);
+      oacc[0] = fmaf(p, v0.x, oacc[0]);
+      oacc[1] = fmaf(p, v0.y, oacc[1]);
+      oacc[2] = fmaf(p, v1.x, oacc[2]);
+      oacc[3] = fmaf(p, v1.y, oacc[3]);
+      oacc[4] = fmaf(p, v2.x, oacc[4]);
+      oacc[5] = fmaf(p, v2.y, oacc[5]);
+      oacc[6] = fmaf(p, v3.x, oacc[6]);
+      oacc[7] = fmaf(p, v3.y, oacc[7]);
+    }
+    __syncthreads();  // sc[] and redf[] are reused by the next pass
+  }
+  // reduce the RPI row groups
+#pragma unroll
+  for (int e = 0; e < 8; ++e) osum[vrow][vch * 8 + e] = oacc[e];
+  __syncthreads();
+  float o = 0.f;  // thread j < HD owns output dim j
+  if (tid < HD) {
+#pragma unroll
+    for (int r = 0; r < RPI; ++r) o += osum[r][tid];
+  }
+
+  const size_t slot_id = (size_t)i * gridDim.y + b;
+  if (nsplit == 1) {
+    if (tid < HD) a.ctx[bh * HD + tid] = __float2half_rn(l_run > 0.f ? o / l_run : 0.f);
+    return;
+  }
+  float *part = a.partial + (slot_id * nsplit + sp) * (HD + 2);
+  if (tid < HD) __stcg(part + 2 + tid, o);
+  if (tid == 0) {
+    __stcg(part, m_run);
+    __stcg(part + 1, l_run);
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned ticket = atomicAdd(&a.counters[slot_id], 1u);
+    is_last = (ticket == (unsigned)nsplit - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (tid < HD) {
+    const float *p0 = a.partial + slot_id * nsplit * (HD + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, __ldcg(p0 + (size_t)s * (HD + 2)));
+    float l = 0.f, acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = __ldcg(p0 + (size_t)s * (HD + 2));
+      if (ms == -INFINITY) continue;
+      const float w = __expf(ms - m);
+      l += w * __ldcg(p0 + (size_t)s * (HD + 2) + 1);
+      acc += w * __ldcg(p0 + (size_t)s * (HD + 2) + 2 + tid);
+    }
+    a.ctx[bh * HD + tid] = __float2half_rn(l > 0.f ? acc / l : 0.f);
+  }
+  if (tid == 0) a.counters[slot_id] = 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Output projection over selected heads, weight in the reference's (d, nheads, hd) layout: every output
+// row n reads one contiguous hd*2-byte segment per selected head. A warp owns OP_ROWS output rows;
+// hd/8 lanes cover one segment, so 32/(hd/8) segments are fetched per warp instruction.
+// ------------------------------------------------------------------------------------------
+constexpr int OP_THREADS = 256;
+constexpr int OP_ROWS = 4;
+
+template <int HD, int B>
+__global__ void __launch_bounds__(OP_THREADS)
+out_proj_sparse_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
+                       const int *__restrict__ head_idx, const int *__restrict__ n_active_dev,
+                       const __half *__restrict__ bias, int d, int nheads, int nnz) {
+  constexpr int LPS = HD / 8;      // lanes per segment
+  constexpr int SEGS = WARP / LPS; // segments per warp load
+  const int tid = threadIdx.x, lane = tid % WARP;
+  const int gw = (blockIdx.x * OP_THREADS + tid) / WARP;
+  const int n0 = gw * OP_ROWS;
+  if (n0 >= d) return;
+  int n_eff = nnz;
+  if (n_active_dev) n_eff = min(nnz, *n_active_dev);
+  const int seg = lane / LPS, c = lane % LPS;
+  const size_t row_stride = (size_t)nheads * HD;
+
+  float acc[OP_ROWS][B];
+#pragma unroll
+  for (int r = 0; r < OP_ROWS; ++r)
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+
+  for (int i = seg; i < n_eff; i += SEGS) {
+    const int h = head_idx[i];
+    uint4 wv[OP_ROWS];
+#pragma unroll
+    for (int r = 0; r < OP_ROWS; ++r) {
+      const int n = n0 + r;
+      wv[r] = (n < d) ? ld_stream16(W + (size_t)n * row_stride + (size_t)h * HD + c * 8)
+                      : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const uint4 xv = ld_cached16(X + ((size_t)b * nheads + h) * HD + c * 8);
+#pragma unroll
+      for (int r = 0; r < OP_ROWS; ++r) acc[r][b] = dot8(wv[r], xv, acc[r][b]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < OP_ROWS; ++r)
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < OP_ROWS; ++r) {
+      const int n = n0 + r;
+      if (n < d) {
+        const float bv = bias ? __half2float(bias[n]) : 0.f;
+#pragma unroll
+        for (int b = 0; b < B; ++b) Y[(size_t)b * d + n] = __float2half_rn(acc[r][b] + bv);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// cache scatter operators (reference semantics)
+// ------------------------------------------------------------------------------------------
+template <bool IS_K>
+__global__ void cache_copy_sparse_kernel(const __half *__restrict__ src, __half *__restrict__ cache,
+                                         const int *__restrict__ head_idx,
+                                         const int *__restrict__ seqlen_idx,
+                                         const int *__restrict__ padding, int T, int nheads, int hd,
+                                         int S, long long ld_t, long long ld_h) {
+  const int i = blockIdx.x, t = blockIdx.y;
+  const int pos0 = seqlen_idx[i * T + t];
+  if (pos0 < 0) return;
+  const int h = head_idx[i];
+  const int pos = pos0 + (padding ? *padding : 0);
+  if (pos < 0 || pos >= S) return;
+  // the source row is the token row named by seqlen_idx (the reference indexes k with it too)
+  const __half *s = src + (size_t)pos0 * ld_t + (size_t)h * ld_h;
+  for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+    if (IS_K)
+      cache[(((size_t)h * (hd / 8) + j / 8) * S + pos) * 8 + j % 8] = s[j];
+    else
+      cache[((size_t)h * S + pos) * hd + j] = s[j];
+  }
+}
+
+}  // namespace djv
+
+using namespace djv;
+
+static int pick_wpr(long long rows, int nchunks) {
+  const long long target = (long long)sm_count() * 32;
+  int wpr = 1;
+  while (wpr < 8 && rows * wpr < target && nchunks >= 64 * wpr * 2) wpr *= 2;
+  return wpr;
+}
+
+template <int MODE>
+static void launch_qkv(const QkvArgs &a, int capacity_heads, int wpr, cudaStream_t st) {
+  const int grid = capacity_heads * 3 * (a.hd / QKV_RPB);
+  switch (wpr) {
+    case 1: qkv_sparse_kernel<MODE, 1><<<grid, QKV_THREADS, 0, st>>>(a); break;
+    case 2: qkv_sparse_kernel<MODE, 2><<<grid, QKV_THREADS, 0, st>>>(a); break;
+    case 4: qkv_sparse_kernel<MODE, 4><<<grid, QKV_THREADS, 0, st>>>(a); break;
+    default: qkv_sparse_kernel<MODE, 8><<<grid, QKV_THREADS, 0, st>>>(a); break;
+  }
+}
+
+static int check_hd(const char *op, int hd, int d) {
+  DJV_REQUIRE(hd == 32 || hd == 64 || hd == 128, "%s: head_dim %d not in {32,64,128}", op, hd);
+  DJV_REQUIRE(d >= 8 && d % 8 == 0, "%s: hidden dim %d must be a multiple of 8", op, d);
+  return DJV_OK;
+}
+
+extern "C" int djv_qkv_proj_sparse(void *y, const void *w, const void *x, const int32_t *head_idx,
+                                   const int32_t *batch_idx, const void *bias, int T, int d,
+                                   int nheads, int hd, int nnz, void *stream) {
+  DJV_REQUIRE(y && w && x && head_idx && batch_idx, "qkv_proj_sparse: null pointer");
+  int rc = check_hd("qkv_proj_sparse", hd, d);
+  if (rc) return rc;
+  DJV_REQUIRE(T >= 1 && T <= DJV_KV_WINDOW, "qkv_proj_sparse: %d token rows outside [1,16]", T);
+  DJV_REQUIRE(nnz >= 0 && nnz <= nheads, "qkv_proj_sparse: nnz=%d outside [0,%d]", nnz, nheads);
+  DJV_REQUIRE(aligned16(w) && aligned16(x), "qkv_proj_sparse: w and x must be 16-byte aligned");
+  if (nnz == 0) return DJV_OK;
+  QkvArgs a{};
+  a.w = static_cast<const __half *>(w);
+  a.bias = static_cast<const __half *>(bias);
+  a.x = static_cast<const __half *>(x);
+  a.d = d; a.nheads = nheads; a.hd = hd; a.nnz = nnz; a.T = T;
+  a.y = static_cast<__half *>(y);
+  a.head_idx = head_idx;
+  a.batch_idx = batch_idx;
+  launch_qkv<0>(a, nnz, pick_wpr((long long)nnz * 3 * hd, d / 8), static_cast<cudaStream_t>(stream));
+  count_launch();
+  return check_launch("qkv_proj_sparse");
+}
+
+template <int HD>
+static int launch_out_proj(int B, __half *Y, const __half *W, const __half *X, const int *head_idx,
+                           const int *n_active_dev, const __half *bias, int d, int nheads, int nnz,
+                           cudaStream_t st) {
+  const int warps = ceil_div(d, OP_ROWS);
+  const int grid = ceil_div(warps * WARP, OP_THREADS);
+#define DJV_OP(B_) \
+  out_proj_sparse_kernel<HD, B_><<<grid, OP_THREADS, 0, st>>>(Y, W, X, head_idx, n_active_dev, bias, d, nheads, nnz)
+  switch (B) {
+    case 1: DJV_OP(1); break;
+    case 2: DJV_OP(2); break;
+    case 3: DJV_OP(3); break;
+    case 4: DJV_OP(4); break;
+    default: set_error("out_proj_sparse: internal batch slice %d", B); return DJV_ERR_INVALID;
+  }
+#undef DJV_OP
+  return DJV_OK;
+}
+
+extern "C" int djv_out_proj_sparse(void *y, const void *w, const void *x, const int32_t *head_idx,
+                                   const int32_t *n_active_dev, const void *bias, int B, int d,
+                                   int nheads, int hd, int nnz, void *stream) {
+  DJV_REQUIRE(y && w && x && head_idx, "out_proj_sparse: null pointer");
+  int rc = check_hd("out_proj_sparse", hd, d);
+  if (rc) return rc;
+  DJV_REQUIRE(B >= 1 && B <= 16, "out_proj_sparse: batch %d outside [1,16]", B);
+  DJV_REQUIRE(nnz >= 0 && nnz <= nheads, "out_proj_sparse: nnz=%d outside [0,%d]", nnz, nheads);
+  DJV_REQUIRE(aligned16(w) && aligned16(x), "out_proj_sparse: w and x must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int b0 = 0; b0 < B; b0 += 4) {
+    const int bs = (B - b0 < 4) ? (B - b0) : 4;
+    __half *Y = static_cast<__half *>(y) + (size_t)b0 * d;
+    const __half *X = static_cast<const __half *>(x) + (size_t)b0 * nheads * hd;
+    const __half *W = static_cast<const __half *>(w);
+    const __half *bi = static_cast<const __half *>(bias);
+    if (hd == 128) rc = launch_out_proj<128>(bs, Y, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st);
+    else if (hd == 64) rc = launch_out_proj<64>(bs, Y, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st);
+    else rc = launch_out_proj<32>(bs, Y, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st);
+    if (rc) return rc;
+    count_launch();
+  }
+  return check_launch("out_proj_sparse");
+}
+
+static int cache_copy(bool is_k, const void *src, void *cache, const int32_t *head_idx,
+                      const int32_t *seqlen_idx, const int32_t *padding, int T, int nheads, int hd,
+                      int S, int nnz, long long ld_t, long long ld_h, void *stream) {
+  const char *op = is_k ? "k_cache_copy_sparse" : "v_cache_copy_sparse";
+  DJV_REQUIRE(src && cache && head_idx && seqlen_idx, "%s: null pointer", op);
+  DJV_REQUIRE(hd % 8 == 0 && hd >= 8, "%s: head_dim %d must be a multiple of 8", op, hd);
+  DJV_REQUIRE(T >= 1 && T <= DJV_KV_WINDOW, "%s: %d token rows outside [1,16]", op, T);
+  DJV_REQUIRE(nnz >= 0 && nnz <= nheads && S >= 1, "%s: bad nnz/S", op);
+  if (nnz == 0) return DJV_OK;
+  dim3 grid(nnz, T);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_k)
+    cache_copy_sparse_kernel<true><<<grid, 128, 0, st>>>(static_cast<const __half *>(src),
+                                                         static_cast<__half *>(cache), head_idx,
+                                                         seqlen_idx, padding, T, nheads, hd, S, ld_t, ld_h);
+  else
+    cache_copy_sparse_kernel<false><<<grid, 128, 0, st>>>(static_cast<const __half *>(src),
+                                                          static_cast<__half *>(cache), head_idx,
+                                                          seqlen_idx, padding, T, nheads, hd, S, ld_t, ld_h);
+  count_launch();
+  return check_launch(op);
+}
+
+extern "C" int djv_k_cache_copy_sparse(const void *k, void *k_cache, const int32_t *head_idx,
+                                       const int32_t *seqlen_idx, const int32_t *padding, int T,
+                                       int nheads, int hd, int S, int nnz, long long ld_t,
+                                       long long ld_h, void *stream) {
+  return cache_copy(true, k, k_cache, head_idx, seqlen_idx, padding, T, nheads, hd, S, nnz, ld_t, ld_h, stream);
+}
+extern "C" int djv_v_cache_copy_sparse(const void *v, void *v_cache, const int32_t *head_idx,
+                                       const int32_t *seqlen_idx, const int32_t *padding, int T,
+                                       int nheads, int hd, int S, int nnz, long long ld_t,
+                                       long long ld_h, void *stream) {
+  return cache_copy(false, v, v_cache, head_idx, seqlen_idx, padding, T, nheads, hd, S, nnz, ld_t, ld_h, stream);
+}
+
+extern "C" int djv_attn_state_reset(int32_t *state, int nheads, int prompt_len, void *stream) {
+  DJV_REQUIRE(state && nheads >= 1 && nheads <= 1024 && prompt_len >= 0, "attn_state_reset: bad argument");
+  attn_state_reset_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(state, nheads, prompt_len);
+  count_launch();
+  return check_launch("attn_state_reset");
+}
+
+static int attn_splits(int S) {
+  int s = ceil_div(S, 128);
+  if (s > 16) s = 16;
+  if (s < 1) s = 1;
+  return s;
+}
+
+static size_t attn_scratch_bytes(int slots, int B, int hd, int S) {
+  return AT_COUNTER_BYTES + (size_t)slots * B * attn_splits(S) * (hd + 2) * sizeof(float);
+}
+
+static int launch_attn(AttnArgs a, int slots, int B, void *scratch, size_t scratch_bytes, cudaStream_t st,
+                       const char *op) {
+  const int nsplit = attn_splits(a.S);
+  const size_t need = attn_scratch_bytes(slots, B, a.hd, a.S);
+  if (nsplit > 1) {
+    if (!scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
+      set_error("%s: scratch needs %zu bytes, 256-byte aligned (got %zu)", op, need, scratch_bytes);
+      return DJV_ERR_SCRATCH;
+    }
+    DJV_REQUIRE((size_t)slots * B * sizeof(unsigned) <= AT_COUNTER_BYTES, "%s: too many (head,batch) slots", op);
+    a.counters = reinterpret_cast<unsigned *>(scratch);
+    a.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + AT_COUNTER_BYTES);
+  }
+  dim3 grid(slots, B, nsplit);
+  if (a.hd == 128) decode_attn_kernel<128><<<grid, AT_THREADS, 0, st>>>(a);
+  else if (a.hd == 64) decode_attn_kernel<64><<<grid, AT_THREADS, 0, st>>>(a);
+  else decode_attn_kernel<32><<<grid, AT_THREADS, 0, st>>>(a);
+  count_launch();
+  return DJV_OK;
+}
+
+extern "C" size_t djv_attn_step_scratch_bytes(int nheads, int hd, int S) {
+  if (nheads < 1 || hd < 8 || S < 1) return 0;
+  return attn_scratch_bytes(nheads, 1, hd, S);
+}
+
+extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, const void *x,
+                             void *x_ring, void *k_cache, void *v_cache, int32_t *state,
+                             const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
+                             float softmax_scale, void *scratch, size_t scratch_bytes, void *stream) {
+  DJV_REQUIRE(ctx && q_out && wqkv && x && x_ring && k_cache && v_cache && state, "attn_step: null pointer");
+  int rc = check_hd("attn_step", hd, d);
+  if (rc) return rc;
+  DJV_REQUIRE(nheads >= 1 && nheads <= 1024, "attn_step: nheads=%d outside [1,1024]", nheads);
+  DJV_REQUIRE(head_idx == nullptr || (nnz >= 0 && nnz <= nheads), "attn_step: nnz=%d outside [0,%d]", nnz, nheads);
+  DJV_REQUIRE(S >= 1, "attn_step: cache capacity S=%d", S);
+  DJV_REQUIRE(aligned16(wqkv) && aligned16(x) && aligned16(x_ring) && aligned16(k_cache) && aligned16(v_cache),
+              "attn_step: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  attn_prep_kernel<<<1, 1024, 0, st>>>(state, head_idx, head_idx ? nnz : 0, static_cast<const __half *>(x),
+                                       static_cast<__half *>(x_ring), d, nheads, S);
+  count_launch();
+  QkvArgs a{};
+  a.w = static_cast<const __half *>(wqkv);
+  a.bias = static_cast<const __half *>(bqkv);
+  a.x = static_cast<const __half *>(x_ring);
+  a.d = d; a.nheads = nheads; a.hd = hd; a.nnz = nheads; a.T = DJV_KV_WINDOW;
+  a.state = state;
+  a.q_out = static_cast<__half *>(q_out);
+  a.k_cache = static_cast<__half *>(k_cache);
+  a.v_cache = static_cast<__half *>(v_cache);
+  a.S = S;
+  const int typical = head_idx ? (nnz > 0 ? nnz : 1) : nheads;
+  launch_qkv<1>(a, nheads, pick_wpr((long long)typical * 3 * hd, d / 8), st);
+  count_launch();
+  AttnArgs t{};
+  t.ctx = static_cast<__half *>(ctx);
+  t.q = static_cast<const __half *>(q_out);
+  t.k_cache = a.k_cache;
+  t.v_cache = a.v_cache;
+  t.state = state;
+  t.nnz = nheads; t.nheads = nheads; t.hd = hd; t.S = S; t.len = 0;
+  t.scale = softmax_scale;
+  rc = launch_attn(t, nheads, 1, scratch, scratch_bytes, st, "attn_step");
+  if (rc) return rc;
+  return check_launch("attn_step");
+}
+
+extern "C" int djv_attn_step_finish(int32_t *state, int nheads, void *stream) {
+  DJV_REQUIRE(state && nheads >= 1, "attn_step_finish: bad argument");
+  attn_finish_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(state);
+  count_launch();
+  return check_launch("attn_step_finish");
+}
+
+extern "C" size_t djv_decode_attn_scratch_bytes(int nnz, int B, int hd, int S) {
+  if (nnz < 1 || B < 1 || hd < 8 || S < 1) return 0;
+  return attn_scratch_bytes(nnz, B, hd, S);
+}
+
+extern "C" int djv_decode_attn(void *ctx, const void *q, const void *k_cache, const void *v_cache,
+                               const int32_t *head_idx, int nnz, int B, int nheads, int hd, int S,
+                               int len, float softmax_scale, void *scratch, size_t scratch_bytes,
+                               void *stream) {
+  DJV_REQUIRE(ctx && q && k_cache && v_cache, "decode_attn: null pointer");
+  DJV_REQUIRE(hd == 32 || hd == 64 || hd == 128, "decode_attn: head_dim %d not in {32,64,128}", hd);
+  DJV_REQUIRE(B >= 1 && nheads >= 1 && S >= 1 && len >= 0 && len <= S, "decode_attn: bad sizes");
+  const int slots = head_idx ? nnz : nheads;
+  DJV_REQUIRE(slots >= 0 && slots <= nheads, "decode_attn: nnz=%d outside [0,%d]", nnz, nheads);
+  DJV_REQUIRE(aligned16(k_cache) && aligned16(v_cache), "decode_attn: caches must be 16-byte aligned");
+  if (slots == 0) return DJV_OK;
+  AttnArgs t{};
+  t.ctx = static_cast<__half *>(ctx);
+  t.q = static_cast<const __half *>(q);
+  t.k_cache = static_cast<const __half *>(k_cache);
+  t.v_cache = static_cast<const __half *>(v_cache);
+  t.head_idx = head_idx;
+  t.nnz = slots; t.nheads = nheads; t.hd = hd; t.S = S; t.len = len;
+  t.scale = softmax_scale;
+  int rc = launch_attn(t, slots, B, scratch, scratch_bytes, static_cast<cudaStream_t>(stream), "decode_attn");
+  if (rc) return rc;
+  return check_launch("decode_attn");
+}

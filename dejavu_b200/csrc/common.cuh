@@ -1,0 +1,97 @@
+// Shared helpers for the sm_100a kernels: error reporting, vector loads, reductions.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/dejavu_b200.h"
+
+namespace djv {
+
+// ---- host side ----------------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+void count_launch(int n = 1);
+int check_launch(const char *what);  // cudaGetLastError -> status
+
+#define DJV_REQUIRE(cond, ...)          \
+  do {                                  \
+    if (!(cond)) {                      \
+      djv::set_error(__VA_ARGS__);      \
+      return DJV_ERR_INVALID;           \
+    }                                   \
+  } while (0)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+int sm_count();  // multiprocessors of the current device (cached per device)
+
+// ---- device side --------------------------------------------------------------------------
+constexpr int WARP = 32;
+
+// 16-byte read-only load that does not pollute L1 (weights are streamed exactly once).
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// 16-byte cached load (activations, small reused vectors).
+__device__ __forceinline__ uint4 ld_cached16(const void *p) {
+  return __ldg(reinterpret_cast<const uint4 *>(p));
+}
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+  unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ float2 h2f(uint32_t u) {
+  __half2 h = *reinterpret_cast<__half2 *>(&u);
+  return __half22float2(h);
+}
+
+// dot of 8 fp16 (packed in a uint4) with 8 fp16 (packed in a uint4), fp32 accumulate
+__device__ __forceinline__ float dot8(const uint4 &a, const uint4 &b, float acc) {
+  float2 a0 = h2f(a.x), a1 = h2f(a.y), a2 = h2f(a.z), a3 = h2f(a.w);
+  float2 b0 = h2f(b.x), b1 = h2f(b.y), b2 = h2f(b.z), b3 = h2f(b.w);
+  acc = fmaf(a0.x, b0.x, acc);
+  acc = fmaf(a0.y, b0.y, acc);
+  acc = fmaf(a1.x, b1.x, acc);
+  acc = fmaf(a1.y, b1.y, acc);
+  acc = fmaf(a2.x, b2.x, acc);
+  acc = fmaf(a2.y, b2.y, acc);
+  acc = fmaf(a3.x, b3.x, acc);
+  acc = fmaf(a3.y, b3.y, acc);
+  return acc;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int ACT>
+__device__ __forceinline__ float apply_act(float v) {
+  if (ACT == DJV_ACT_RELU) return fmaxf(v, 0.f);
+  if (ACT == DJV_ACT_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  if (ACT == DJV_ACT_GELU_APPROX)
+    return 0.5f * v * (1.f + tanhf(0.79788456080286536f * v * (1.f + 0.044715f * v * v)));
+  if (ACT == DJV_ACT_SQUARED_RELU) {
+    float r = fmaxf(v, 0.f);
+    return r * r;
+  }
+  return v;
+}
+
+}  // namespace djv

@@ -1,0 +1,490 @@
+// Gather GEMV kernels for the sparse MLP (and, with idx == NULL, every dense GEMV of the decode step).
+//
+// Both kernels are bound by HBM bandwidth: each gathered weight row is read exactly once with 128-bit
+// loads that bypass L1, accumulated in fp32 and rounded to fp16 once.
+//
+//   rowdot  : y[b,m] = act(w[idx[m],:] . x[b,:] + bias[idx[m]])      one row -> one output  (fc1)
+//   rowaxpy : y[b,:] = sum_m x[b,m] * w[idx[m],:] + bias             one row -> a d-vector  (fc2)
+//
+// Algorithmic bytes per launch (fp16, int32 idx):
+//   rowdot  : M*N*2 + M*2 (bias) + M*4 (idx) + B*N*2 (x) + B*M*2 (y)
+//   rowaxpy : M*N*2 + B*M*2 (x) + N*2 (bias) + B*N*2 (y)
+#include "common.cuh"
+
+namespace djv {
+
+__device__ __forceinline__ long long load_index(const void *idx, int m, int idx64) {
+  if (idx == nullptr) return m;
+  return idx64 ? reinterpret_cast<const long long *>(idx)[m]
+               : static_cast<long long>(reinterpret_cast<const int *>(idx)[m]);
+}
+
+// -------------------------------------------------------------------------------------------
+// rowdot. A block has 8 warps split into 8/WPR groups of WPR warps; a group owns ROWS rows at a
+// time and its 32*WPR lanes stride over the 16-byte chunks of those rows, U chunks in flight per
+// lane per row. x is read through L1 (it is tiny and reused by every warp); weights bypass L1.
+// Small M uses large WPR so that the whole device has loads in flight for a handful of rows.
+// -------------------------------------------------------------------------------------------
+constexpr int RD_THREADS = 256;
+constexpr int RD_WARPS = RD_THREADS / WARP;
+
+template <int B, int ACT, int WPR, int ROWS, int U>
+__global__ void __launch_bounds__(RD_THREADS)
+rowdot_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
+              const void *__restrict__ idx, const __half *__restrict__ bias, int M, int N,
+              long long ldw, int idx64) {
+  constexpr int GROUPS = RD_WARPS / WPR;
+  constexpr int GLANES = WARP * WPR;
+  __shared__ float red[WPR > 1 ? RD_WARPS * ROWS * B : 1];
+
+  const int tid = threadIdx.x;
+  const int warp = tid / WARP, lane = tid % WARP;
+  const int group = warp / WPR, wig = warp % WPR;
+  const int glane = wig * WARP + lane;
+  const int nchunks = N / 8;
+  const uint4 *Xv = reinterpret_cast<const uint4 *>(X);
+
+  const int rows_per_pass = gridDim.x * GROUPS * ROWS;
+  // trip count is uniform over the block so that __syncthreads below is legal
+  for (int base = blockIdx.x * GROUPS * ROWS; base < M; base += rows_per_pass) {
+    const int m0 = base + group * ROWS;
+    const uint4 *wp[ROWS];
+    float bv[ROWS];
+#pragma unroll
+    for (int j = 0; j < ROWS; ++j) {
+      const int m = m0 + j;
+      const bool ok = m < M;
+      const long long r = ok ? load_index(idx, m, idx64) : 0;
+      wp[j] = reinterpret_cast<const uint4 *>(W + r * ldw);
+      bv[j] = (bias != nullptr && ok) ? __half2float(bias[r]) : 0.f;
+      if (!ok) wp[j] = nullptr;
+    }
+    float acc[ROWS][B];
+#pragma unroll
+    for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+      for (int b = 0; b < B; ++b) acc[j][b] = 0.f;
+
+    for (int c0 = glane; c0 < nchunks; c0 += GLANES * U) {
+      uint4 wv[ROWS][U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + u * GLANES;
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+          if (c < nchunks && wp[j] != nullptr)
+            wv[j][u] = ld_stream16(wp[j] + c);
+          else
+            wv[j][u] = make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + u * GLANES;
+        if (c < nchunks) {
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            const uint4 xv = ld_cached16(Xv + (size_t)b * nchunks + c);
+#pragma unroll
+            for (int j = 0; j < ROWS; ++j) acc[j][b] = dot8(wv[j][u], xv, acc[j][b]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+      for (int b = 0; b < B; ++b) acc[j][b] = warp_sum(acc[j][b]);
+
+    if (WPR > 1) {
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+          for (int b = 0; b < B; ++b) red[(warp * ROWS + j) * B + b] = acc[j][b];
+      }
+      __syncthreads();
+      if (wig == 0 && lane == 0) {
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            float s = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < WPR; ++w2) s += red[((group * WPR + w2) * ROWS + j) * B + b];
+            acc[j][b] = s;
+          }
+      }
+    }
+    if (wig == 0 && lane == 0) {
+#pragma unroll
+      for (int j = 0; j < ROWS; ++j) {
+        const int m = m0 + j;
+        if (m < M) {
+#pragma unroll
+          for (int b = 0; b < B; ++b)
+            Y[(size_t)b * M + m] = __float2half_rn(apply_act<ACT>(acc[j][b] + bv[j]));
+        }
+      }
+    }
+    if (WPR > 1) __syncthreads();  // red[] is reused by the next pass
+  }
+}
+
+struct RowdotPlan {
+  int wpr, rows, grid;
+};
+
+static RowdotPlan plan_rowdot(int M, int N, int B) {
+  const int sms = sm_count();
+  const int nchunks = N / 8;
+  const int rows = (B <= 2) ? 2 : 1;
+  // enough warps for ~32 resident warps per SM, but at least one chunk per lane
+  const long long target_warps = (long long)sms * 32;
+  int wpr = 1;
+  while (wpr < 8 && (long long)ceil_div(M, rows) * wpr < target_warps && nchunks >= 64 * wpr * 2)
+    wpr *= 2;
+  const int groups = RD_WARPS / wpr;
+  int grid = ceil_div(M, groups * rows);
+  const int cap = sms * 6;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  return {wpr, rows, grid};
+}
+
+template <int B, int ACT>
+static void launch_rowdot(const RowdotPlan &p, __half *Y, const __half *W, const __half *X,
+                          const void *idx, const __half *bias, int M, int N, long long ldw,
+                          int idx64, cudaStream_t st) {
+#define DJV_RD(WPR_, ROWS_)                                                               \
+  rowdot_kernel<B, ACT, WPR_, ROWS_, 4><<<p.grid, RD_THREADS, 0, st>>>(Y, W, X, idx, bias, M, N, \
+                                                                       ldw, idx64)
+  constexpr int R = (B <= 2) ? 2 : 1;
+  switch (p.wpr) {
+    case 1: DJV_RD(1, R); break;
+    case 2: DJV_RD(2, R); break;
+    case 4: DJV_RD(4, R); break;
+    default: DJV_RD(8, R); break;
+  }
+#undef DJV_RD
+}
+
+template <int B>
+static int dispatch_act(const RowdotPlan &p, int act, __half *Y, const __half *W, const __half *X,
+                        const void *idx, const __half *bias, int M, int N, long long ldw, int idx64,
+                        cudaStream_t st) {
+  switch (act) {
+    case DJV_ACT_ID: launch_rowdot<B, DJV_ACT_ID>(p, Y, W, X, idx, bias, M, N, ldw, idx64, st); break;
+    case DJV_ACT_RELU: launch_rowdot<B, DJV_ACT_RELU>(p, Y, W, X, idx, bias, M, N, ldw, idx64, st); break;
+    case DJV_ACT_GELU: launch_rowdot<B, DJV_ACT_GELU>(p, Y, W, X, idx, bias, M, N, ldw, idx64, st); break;
+    case DJV_ACT_GELU_APPROX:
+      launch_rowdot<B, DJV_ACT_GELU_APPROX>(p, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+      break;
+    case DJV_ACT_SQUARED_RELU:
+      launch_rowdot<B, DJV_ACT_SQUARED_RELU>(p, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+      break;
+    default: set_error("gather_gemv: unknown activation %d", act); return DJV_ERR_INVALID;
+  }
+  return DJV_OK;
+}
+
+// One launch handles up to 8 rows of x; larger batches are cut into slices of <= 8 rows
+// (each slice re-reads the gathered rows).
+static int rowdot_slice(int B, int act, __half *Y, const __half *W, const __half *X, const void *idx,
+                        const __half *bias, int M, int N, long long ldw, int idx64, cudaStream_t st) {
+  const RowdotPlan p = plan_rowdot(M, N, B);
+  switch (B) {
+    case 1: return dispatch_act<1>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+    case 2: return dispatch_act<2>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+    case 3: return dispatch_act<3>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+    case 4: return dispatch_act<4>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+    case 5: return dispatch_act<5>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+    case 6: return dispatch_act<6>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+    case 7: return dispatch_act<7>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+    case 8: return dispatch_act<8>(p, act, Y, W, X, idx, bias, M, N, ldw, idx64, st);
+  }
+  set_error("gather_gemv: internal batch slice %d", B);
+  return DJV_ERR_INVALID;
+}
+
+// -------------------------------------------------------------------------------------------
+// rowaxpy. grid = (column tiles, row chunks). A block owns 128*8 = 1024 consecutive columns (one
+// 16-byte chunk per thread) and a contiguous chunk of the index list; it keeps 8*B fp32 sums per
+// thread, writes them to `partial`, and the last block to arrive for a column tile adds the partials
+// in chunk order (deterministic), adds the bias and stores fp16.
+// -------------------------------------------------------------------------------------------
+constexpr int RA_THREADS = 128;
+constexpr int RA_TILE = RA_THREADS * 8;
+constexpr int RA_MAX_RPC = 512;  // rows per chunk held in shared memory
+constexpr int RA_COUNTER_BYTES = 4096;
+
+__device__ __forceinline__ float4 ld_cg_f4(const float *p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <int B>
+__global__ void __launch_bounds__(RA_THREADS)
+rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
+               const void *__restrict__ idx, const __half *__restrict__ bias,
+               float *__restrict__ partial, unsigned *__restrict__ counters, int M, int N,
+               long long ldw, int idx64, int rpc) {
+  __shared__ long long offs[RA_MAX_RPC];
+  __shared__ float xs[B][RA_MAX_RPC];
+  __shared__ int is_last;
+
+  const int tid = threadIdx.x;
+  const int tile = blockIdx.x, mc = blockIdx.y, MC = gridDim.y;
+  const int nchunks = N / 8;
+  const int chunk = tile * RA_THREADS + tid;
+  const bool active = chunk < nchunks;
+  const int m_begin = mc * rpc;
+  const int cnt = min(rpc, M - m_begin);
+
+  for (int i = tid; i < cnt; i += RA_THREADS) {
+    offs[i] = load_index(idx, m_begin + i, idx64) * ldw;
+#pragma unroll
+    for (int b = 0; b < B; ++b) xs[b][i] = __half2float(X[(size_t)b * M + m_begin + i]);
+  }
+  __syncthreads();
+
+  float acc[B][8];
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[b][e] = 0.f;
+
+  constexpr int U = 8;
+  if (active) {
+    const __half *wcol = W + (size_t)chunk * 8;
+    for (int i0 = 0; i0 < cnt; i0 += U) {
+      uint4 wv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u < cnt)
+          wv[u] = ld_stream16(wcol + offs[i0 + u]);
+        else
+          wv[u] = make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u < cnt) {
+          const float2 w0 = h2f(wv[u].x), w1 = h2f(wv[u].y), w2 = h2f(wv[u].z), w3 = h2f(wv[u].w);
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            const float xb = xs[b][i0 + u];
+            acc[b][0] = fmaf(xb, w0.x, acc[b][0]);
+            acc[b][1] = fmaf(xb, w0.y, acc[b][1]);
+            acc[b][2] = fmaf(xb, w1.x, acc[b][2]);
+            acc[b][3] = fmaf(xb, w1.y, acc[b][3]);
+            acc[b][4] = fmaf(xb, w2.x, acc[b][4]);
+            acc[b][5] = fmaf(xb, w2.y, acc[b][5]);
+            acc[b][6] = fmaf(xb, w3.x, acc[b][6]);
+            acc[b][7] = fmaf(xb, w3.y, acc[b][7]);
+          }
+        }
+      }
+    }
+  }
+
+  if (MC > 1) {
+    if (active) {
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        float *p = partial + ((size_t)mc * B + b) * N + (size_t)chunk * 8;
+        __stcg(reinterpret_cast<float4 *>(p), make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]));
+        __stcg(reinterpret_cast<float4 *>(p) + 1,
+               make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]));
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned ticket = atomicAdd(&counters[tile], 1u);
+      is_last = (ticket == (unsigned)MC - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (active) {
+#pragma unroll
+      for (int b = 0; b < B; ++b)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[b][e] = 0.f;
+      for (int c = 0; c < MC; ++c) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const float *p = partial + ((size_t)c * B + b) * N + (size_t)chunk * 8;
+          const float4 lo = ld_cg_f4(p), hi = ld_cg_f4(p + 4);
+          acc[b][0] += lo.x; acc[b][1] += lo.y; acc[b][2] += lo.z; acc[b][3] += lo.w;
+          acc[b][4] += hi.x; acc[b][5] += hi.y; acc[b][6] += hi.z; acc[b][7] += hi.w;
+        }
+      }
+    }
+    if (tid == 0) counters[tile] = 0;  // ready for the next launch
+  }
+
+  if (active) {
+    float bz[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) bz[e] = 0.f;
+    if (bias != nullptr) {
+      const uint4 bvv = ld_cached16(bias + (size_t)chunk * 8);
+      const float2 b0 = h2f(bvv.x), b1 = h2f(bvv.y), b2 = h2f(bvv.z), b3 = h2f(bvv.w);
+      bz[0] = b0.x; bz[1] = b0.y; bz[2] = b1.x; bz[3] = b1.y;
+      bz[4] = b2.x; bz[5] = b2.y; bz[6] = b3.x; bz[7] = b3.y;
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      __half2 o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        o[e] = __floats2half2_rn(acc[b][2 * e] + bz[2 * e], acc[b][2 * e + 1] + bz[2 * e + 1]);
+      *reinterpret_cast<uint4 *>(Y + (size_t)b * N + (size_t)chunk * 8) =
+          *reinterpret_cast<uint4 *>(o);
+    }
+  }
+}
+
+struct RowaxpyPlan {
+  int tiles, mc, rpc;
+};
+
+static RowaxpyPlan plan_rowaxpy(int M, int N) {
+  const int sms = sm_count();
+  const int tiles = ceil_div(N / 8, RA_THREADS);
+  int mc = ceil_div(sms * 6, tiles);          // ~6 blocks of 128 threads per SM
+  const int min_rows = 8;                     // at least one full unroll of rows per block
+  if (mc > ceil_div(M, min_rows)) mc = ceil_div(M, min_rows);
+  if (mc < 1) mc = 1;
+  int rpc = ceil_div(M, mc);
+  if (rpc > RA_MAX_RPC) rpc = RA_MAX_RPC;
+  if (rpc < 1) rpc = 1;
+  mc = ceil_div(M, rpc);
+  if (mc < 1) mc = 1;
+  return {tiles, mc, rpc};
+}
+
+static size_t rowaxpy_scratch_bytes(int B, int N, int M) {
+  const RowaxpyPlan p = plan_rowaxpy(M, N);
+  return RA_COUNTER_BYTES + (size_t)p.mc * B * N * sizeof(float);
+}
+
+template <int B>
+static void launch_rowaxpy(const RowaxpyPlan &p, __half *Y, const __half *W, const __half *X,
+                           const void *idx, const __half *bias, float *partial, unsigned *counters,
+                           int M, int N, long long ldw, int idx64, cudaStream_t st) {
+  dim3 grid(p.tiles, p.mc);
+  rowaxpy_kernel<B><<<grid, RA_THREADS, 0, st>>>(Y, W, X, idx, bias, partial, counters, M, N, ldw,
+                                                 idx64, p.rpc);
+}
+
+static int rowaxpy_slice(int B, __half *Y, const __half *W, const __half *X, const void *idx,
+                         const __half *bias, void *scratch, int M, int N, long long ldw, int idx64,
+                         cudaStream_t st) {
+  const RowaxpyPlan p = plan_rowaxpy(M, N);
+  unsigned *counters = reinterpret_cast<unsigned *>(scratch);
+  float *partial = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + RA_COUNTER_BYTES);
+  switch (B) {
+    case 1: launch_rowaxpy<1>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
+    case 2: launch_rowaxpy<2>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
+    case 3: launch_rowaxpy<3>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
+    case 4: launch_rowaxpy<4>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
+    default: set_error("gather_transposed_gemv: internal batch slice %d", B); return DJV_ERR_INVALID;
+  }
+  return DJV_OK;
+}
+
+// Zero rows selected (M == 0): y = bias (or 0).
+__global__ void bias_fill_kernel(__half *Y, const __half *bias, int B, int N) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B * N) Y[i] = bias ? bias[i % N] : __float2half(0.f);
+}
+
+}  // namespace djv
+
+using namespace djv;
+
+static int check_common(const char *op, const void *y, const void *w, const void *x, int B, int N,
+                        int M, long long ldw) {
+  // with an empty index list there is nothing to read from x (and, for fc1, nothing to write)
+  DJV_REQUIRE(w && (M == 0 || (y && x)), "%s: null pointer", op);
+  DJV_REQUIRE(B >= 1 && B <= DJV_MAX_BATCH, "%s: batch %d outside [1,%d]", op, B, DJV_MAX_BATCH);
+  DJV_REQUIRE(N >= 8 && N % 8 == 0, "%s: N=%d must be a positive multiple of 8", op, N);
+  DJV_REQUIRE(M >= 0, "%s: negative M", op);
+  DJV_REQUIRE(ldw >= N && ldw % 8 == 0, "%s: row stride %lld must be >= N and a multiple of 8", op, ldw);
+  DJV_REQUIRE(aligned16(w), "%s: weight pointer must be 16-byte aligned", op);
+  return DJV_OK;
+}
+
+extern "C" int djv_gather_gemv(void *y, const void *w, const void *x, const void *idx,
+                               const void *bias, int B, int N, int M, long long ldw, int idx_is_64,
+                               int act, void *stream) {
+  int rc = check_common("gather_gemv", y, w, x, B, N, M, ldw);
+  if (rc) return rc;
+  DJV_REQUIRE(aligned16(x), "gather_gemv: x must be 16-byte aligned");
+  DJV_REQUIRE(act >= DJV_ACT_ID && act <= DJV_ACT_SQUARED_RELU, "gather_gemv: unknown activation %d", act);
+  if (M == 0) return DJV_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int b0 = 0; b0 < B; b0 += 8) {
+    const int bs = (B - b0 < 8) ? (B - b0) : 8;
+    rc = rowdot_slice(bs, act, static_cast<__half *>(y) + (size_t)b0 * M, static_cast<const __half *>(w),
+                      static_cast<const __half *>(x) + (size_t)b0 * N, idx,
+                      static_cast<const __half *>(bias), M, N, ldw, idx_is_64, st);
+    if (rc) return rc;
+    count_launch();
+  }
+  return check_launch("gather_gemv");
+}
+
+extern "C" size_t djv_gather_transposed_gemv_scratch_bytes(int B, int N, int M) {
+  if (B < 1 || N < 8 || M < 0) return 0;
+  const int bs = B < 4 ? B : 4;
+  return rowaxpy_scratch_bytes(bs, N, M);
+}
+
+extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x, const void *idx,
+                                          const void *bias, int B, int N, int M, long long ldw,
+                                          int idx_is_64, void *scratch, size_t scratch_bytes,
+                                          void *stream) {
+  int rc = check_common("gather_transposed_gemv", y, w, x, B, N, M, ldw);
+  if (rc) return rc;
+  DJV_REQUIRE(y != nullptr && aligned16(y), "gather_transposed_gemv: y must be non-null and 16-byte aligned");
+  DJV_REQUIRE(bias == nullptr || aligned16(bias), "gather_transposed_gemv: bias must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M == 0) {
+    bias_fill_kernel<<<ceil_div(B * N, 256), 256, 0, st>>>(static_cast<__half *>(y),
+                                                          static_cast<const __half *>(bias), B, N);
+    count_launch();
+    return check_launch("gather_transposed_gemv");
+  }
+  const size_t need = djv_gather_transposed_gemv_scratch_bytes(B, N, M);
+  if (scratch == nullptr || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
+    set_error("gather_transposed_gemv: scratch needs %zu bytes, 256-byte aligned (got %zu)", need,
+              scratch_bytes);
+    return DJV_ERR_SCRATCH;
+  }
+  for (int b0 = 0; b0 < B; b0 += 4) {
+    const int bs = (B - b0 < 4) ? (B - b0) : 4;
+    rc = rowaxpy_slice(bs, static_cast<__half *>(y) + (size_t)b0 * N, static_cast<const __half *>(w),
+                       static_cast<const __half *>(x) + (size_t)b0 * M, idx,
+                       static_cast<const __half *>(bias), scratch, M, N, ldw, idx_is_64, st);
+    if (rc) return rc;
+    count_launch();
+  }
+  return check_launch("gather_transposed_gemv");
+}
+
+extern "C" int djv_mlp_sparse(void *y, void *h, const void *w1, const void *w2t, const void *x,
+                              const void *idx, const void *bias1, const void *bias2, int B, int N,
+                              int M, long long ldw1, long long ldw2t, int idx_is_64, void *scratch,
+                              size_t scratch_bytes, void *stream) {
+  DJV_REQUIRE(h != nullptr || M == 0, "mlp_sparse: h workspace is null");
+  int rc = djv_gather_gemv(h, w1, x, idx, bias1, B, N, M, ldw1, idx_is_64, DJV_ACT_RELU, stream);
+  if (rc) return rc;
+  return djv_gather_transposed_gemv(y, w2t, h, idx, bias2, B, N, M, ldw2t, idx_is_64, scratch,
+                                    scratch_bytes, stream);
+}

@@ -1,0 +1,312 @@
+"""Operator functions with the reference's names, argument meaning and assertions, running the
+sm_100a kernels of libdejavu_b200.so on the current CUDA stream.
+
+Mirrors Dejavu/src/ops/triton/gather_gemv.py (gather_gemv :198-254, gather_transposed_gemv :572-644,
+mlp_sparse :647-657) and Dejavu/src/ops/triton/attention_proj_sparse.py (qkv_proj_sparse :110-194,
+out_proj_sparse :274-338, v_cache_copy_sparse :396-456, k_cache_copy_sparse :525-590).
+Outputs are allocated by the callee with torch.empty, inputs are borrowed, exactly as there.
+There is no CPU path: tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import call
+
+_ACTIVATIONS = ["id", "relu", "gelu", "gelu_approx", "squared_relu"]
+_scratch_cache: dict = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("dejavu_b200 operators run on CUDA tensors only (there is no CPU path)")
+
+
+def _scratch(nbytes: int, device: torch.device) -> torch.Tensor:
+    """Zero-initialised per-(device, stream) workspace; the kernels leave their counters zeroed."""
+    key = (device.index, _stream())
+    buf = _scratch_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(nbytes, 1 << 20)
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _scratch_cache[key] = buf
+    return buf
+
+
+def _idx_args(idx: torch.Tensor):
+    assert idx.dtype in (torch.int32, torch.int64), f"idx must be int32 or int64, got {idx.dtype}"
+    return idx.contiguous(), 1 if idx.dtype == torch.int64 else 0
+
+
+def gather_gemv(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    idx: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    activation: str = "id",
+) -> torch.Tensor:
+    """y = activation(x @ weight[idx, :].T + bias[idx]);  x (batch, N), weight (Z, N), idx (M,),
+    bias (Z,) -> (batch, M) in x.dtype. Indices are not validated (as in the reference)."""
+    assert activation in _ACTIVATIONS
+    Z, N = weight.shape
+    batch, _ = x.shape
+    assert x.shape == (batch, N)
+    assert 1 <= batch <= _lib.MAX_BATCH, f"batch must be in [1, {_lib.MAX_BATCH}]"
+    (M,) = idx.shape
+    _require_cuda(x, weight, idx, bias)
+    x = x.contiguous()
+    if weight.stride(1) > 1:
+        weight = weight.contiguous()
+    assert x.dtype == weight.dtype, f"Input and weight must have the same dtype, got {x.dtype} and {weight.dtype}"
+    assert x.dtype == torch.float16, "only fp16 is implemented"
+    if bias is not None:
+        bias = bias.contiguous()
+        assert bias.shape == (Z,), "Incompatible dimensions in between weight and bias"
+        assert x.dtype == bias.dtype, f"Input and bias must have the same dtype, got {x.dtype} and {bias.dtype}"
+    idx, idx64 = _idx_args(idx)
+    output = torch.empty(batch, M, device=x.device, dtype=x.dtype)
+    call("djv_gather_gemv", output.data_ptr(), weight.data_ptr(), x.data_ptr(), idx.data_ptr(), _ptr(bias),
+         batch, N, M, weight.stride(0), idx64, _lib.ACT[activation], _stream())
+    return output
+
+
+def dense_gemv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               activation: str = "id") -> torch.Tensor:
+    """y = activation(x @ weight.T + bias) with the same kernel (identity index list)."""
+    Z, N = weight.shape
+    batch, _ = x.shape
+    assert x.shape == (batch, N) and 1 <= batch <= _lib.MAX_BATCH
+    _require_cuda(x, weight, bias)
+    x = x.contiguous()
+    if weight.stride(1) > 1:
+        weight = weight.contiguous()
+    assert x.dtype == weight.dtype == torch.float16
+    output = torch.empty(batch, Z, device=x.device, dtype=x.dtype)
+    call("djv_gather_gemv", output.data_ptr(), weight.data_ptr(), x.data_ptr(), None, _ptr(bias),
+         batch, N, Z, weight.stride(0), 0, _lib.ACT[activation], _stream())
+    return output
+
+
+def gather_transposed_gemv(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    idx: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """y = weight[idx, :]^T @ x + bias;  x (batch, M), weight (Z, N), idx (M,), bias (N,) -> (batch, N).
+    Deterministic (fixed summation order), unlike the reference's atomic-add kernel."""
+    Z, N = weight.shape
+    (M,) = idx.shape
+    batch, _ = x.shape
+    assert x.shape == (batch, M)
+    assert 1 <= batch <= _lib.MAX_BATCH, f"batch must be in [1, {_lib.MAX_BATCH}]"
+    _require_cuda(x, weight, idx, bias)
+    x = x.contiguous()
+    if weight.stride(1) > 1:
+        weight = weight.contiguous()
+    assert x.dtype == weight.dtype, f"Input and weight must have the same dtype, got {x.dtype} and {weight.dtype}"
+    assert x.dtype == torch.float16, "only fp16 is implemented"
+    if bias is not None:
+        bias = bias.contiguous()
+        assert bias.shape == (N,), "Incompatible dimensions in between weight and bias"
+        assert x.dtype == bias.dtype, f"Input and bias must have the same dtype, got {x.dtype} and {bias.dtype}"
+    idx, idx64 = _idx_args(idx)
+    output = torch.empty(batch, N, device=x.device, dtype=x.dtype)
+    need = _lib.load().djv_gather_transposed_gemv_scratch_bytes(batch, N, M)
+    scratch = _scratch(need, x.device)
+    call("djv_gather_transposed_gemv", output.data_ptr(), weight.data_ptr(), x.data_ptr(), idx.data_ptr(),
+         _ptr(bias), batch, N, M, weight.stride(0), idx64, scratch.data_ptr(), scratch.numel(), _stream())
+    return output
+
+
+def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None):
+    """x (batch, d); W1 (4d, d); W2t (4d, d) = W2 transposed, contiguous; bias1 (4d); bias2 (d)."""
+    x = gather_gemv(x, W1, idx, bias1, activation="relu")
+    x = gather_transposed_gemv(x, W2t, idx, bias2)
+    return x
+
+
+def qkv_proj_sparse(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    head_idx: torch.Tensor,
+    batch_idx: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """y = einsum("bm,thdm->bthd", x, weight) + bias for the heads in head_idx and the rows named by the
+    non-negative entries of batch_idx; every other entry of y is uninitialised (torch.empty)."""
+    three, nheads, head_dim, hidden_dim = weight.shape
+    assert three == 3
+    assert head_dim in [32, 64, 128]
+    assert hidden_dim % 128 == 0
+    batch_size, _ = x.shape
+    assert batch_size <= 16
+    assert x.shape == (batch_size, hidden_dim)
+    n_active = head_idx.shape[0]
+    assert n_active <= nheads
+    assert head_idx.shape == (n_active,)
+    assert head_idx.dtype == torch.int32
+    assert batch_idx.shape == (n_active, batch_size)
+    assert batch_idx.dtype == torch.int32
+    _require_cuda(x, weight, head_idx, batch_idx, bias)
+    x = x.contiguous()
+    weight = weight.contiguous()
+    head_idx = head_idx.contiguous()
+    batch_idx = batch_idx.contiguous()
+    assert x.dtype == weight.dtype, f"Input and weight must have the same dtype, got {x.dtype} and {weight.dtype}"
+    assert x.dtype == torch.float16, "only fp16 is implemented"
+    if bias is not None:
+        bias = bias.contiguous()
+        assert bias.shape == (3, nheads, head_dim), "Incompatible dimensions in between weight and bias"
+        assert x.dtype == bias.dtype, f"Input and bias must have the same dtype, got {x.dtype} and {bias.dtype}"
+    output = torch.empty(batch_size, 3, nheads, head_dim, device=x.device, dtype=x.dtype)
+    call("djv_qkv_proj_sparse", output.data_ptr(), weight.data_ptr(), x.data_ptr(), head_idx.data_ptr(),
+         batch_idx.data_ptr(), _ptr(bias), batch_size, hidden_dim, nheads, head_dim, n_active, _stream())
+    return output
+
+
+def out_proj_sparse(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    head_idx: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """y = einsum("bhd,nhd->bn", x, weight) + bias over the heads in head_idx only.
+    x (batch, nheads, head_dim), weight (hidden_dim, nheads, head_dim) -> (batch, hidden_dim)."""
+    hidden_dim, nheads, head_dim = weight.shape
+    assert head_dim in [32, 64, 128]
+    assert hidden_dim % 128 == 0
+    batch, _, _ = x.shape
+    assert x.shape == (batch, nheads, head_dim)
+    n_active = head_idx.shape[0]
+    assert head_idx.shape == (n_active,)
+    assert head_idx.dtype == torch.int32
+    assert batch <= 16
+    _require_cuda(x, weight, head_idx, bias)
+    x = x.contiguous()
+    weight = weight.contiguous()
+    head_idx = head_idx.contiguous()
+    assert x.dtype == weight.dtype, f"Input and weight must have the same dtype, got {x.dtype} and {weight.dtype}"
+    assert x.dtype == torch.float16, "only fp16 is implemented"
+    if bias is not None:
+        bias = bias.contiguous()
+        assert bias.shape == (hidden_dim,), "Incompatible dimensions in between weight and bias"
+        assert x.dtype == bias.dtype, f"Input and bias must have the same dtype, got {x.dtype} and {bias.dtype}"
+    output = torch.empty(batch, hidden_dim, device=x.device, dtype=x.dtype)
+    call("djv_out_proj_sparse", output.data_ptr(), weight.data_ptr(), x.data_ptr(), head_idx.data_ptr(), None,
+         _ptr(bias), batch, hidden_dim, nheads, head_dim, n_active, _stream())
+    return output
+
+
+def _cache_copy(fn, src, cache, head_idx, seqlen_idx, padding, S, head_dim):
+    nnz_seqlen, nheads, _ = src.shape
+    n_active = head_idx.shape[0]
+    assert head_dim in [32, 64, 128]
+    assert nnz_seqlen <= 16
+    assert n_active <= nheads
+    assert head_idx.shape == (n_active,)
+    assert head_idx.dtype == torch.int32
+    assert seqlen_idx.shape == (n_active, nnz_seqlen)
+    assert seqlen_idx.dtype == torch.int32
+    assert src.dtype == cache.dtype, f"k/v and cache must have the same dtype, got {src.dtype} and {cache.dtype}"
+    assert src.dtype == torch.float16, "only fp16 is implemented"
+    assert src.stride(-1) == 1 and cache.is_contiguous()
+    _require_cuda(src, cache, head_idx, seqlen_idx, padding)
+    if padding is not None:
+        assert padding.shape == (1,)
+        assert padding.dtype == torch.int32
+    head_idx = head_idx.contiguous()
+    seqlen_idx = seqlen_idx.contiguous()
+    call(fn, src.data_ptr(), cache.data_ptr(), head_idx.data_ptr(), seqlen_idx.data_ptr(), _ptr(padding),
+         nnz_seqlen, nheads, head_dim, S, n_active, src.stride(0), src.stride(1), _stream())
+
+
+def v_cache_copy_sparse(v, v_cache, head_idx, seqlen_idx, padding=None) -> None:
+    """v (nnz_seqlen, nheads, head_dim) -> v_cache (1, nheads, seqlen, head_dim) at the positions
+    seqlen_idx[i, t] + padding for head head_idx[i]; negative positions are skipped."""
+    nnz_seqlen, nheads, head_dim = v.shape
+    _, _, seqlen, _ = v_cache.shape
+    assert v_cache.shape == (1, nheads, seqlen, head_dim)
+    _cache_copy("djv_v_cache_copy_sparse", v, v_cache, head_idx, seqlen_idx, padding, seqlen, head_dim)
+
+
+def k_cache_copy_sparse(k, k_cache, head_idx, seqlen_idx, padding=None) -> None:
+    """k (nnz_seqlen, nheads, head_dim) -> k_cache (1, nheads, head_dim/8, seqlen, 8), same rules."""
+    nnz_seqlen, nheads, head_dim = k.shape
+    _, _, _, seqlen, _ = k_cache.shape
+    assert k_cache.shape == (1, nheads, head_dim // 8, seqlen, 8)
+    _cache_copy("djv_k_cache_copy_sparse", k, k_cache, head_idx, seqlen_idx, padding, seqlen, head_dim)
+
+
+# ---- operators the reference obtains from torch / third-party extensions -------------------------
+
+def topk_indices(scores: torch.Tensor, k: int, dtype: torch.dtype = torch.int64) -> torch.Tensor:
+    """Indices of the k largest entries of a 1-D fp16/fp32 score vector, ascending index order, ties on
+    the k-th value resolved towards the lowest index. Stands in for `scores.topk(k, sorted=False)[1]`
+    (Dejavu/src/models/modules/mha_dejavu.py:1069, 1369, 1506)."""
+    assert scores.dim() == 1 and scores.dtype in (torch.float16, torch.float32)
+    assert dtype in (torch.int32, torch.int64)
+    n = scores.shape[0]
+    assert 0 <= k <= n
+    _require_cuda(scores)
+    scores = scores.contiguous()
+    out = torch.empty(k, dtype=dtype, device=scores.device)
+    a32, a64 = (out.data_ptr(), None) if dtype == torch.int32 else (None, out.data_ptr())
+    call("djv_topk", a32, a64, scores.data_ptr(), n, k, 1 if scores.dtype == torch.float32 else 0, _stream())
+    return out
+
+
+def add_layernorm(x, residual, weight, bias, eps: float, xbias=None):
+    """r = x + residual (+ xbias); y = LayerNorm(r). Returns (y, r). x, residual (batch, d) fp16.
+    Stands in for `residual = dropped + residual; hidden = norm(residual)`
+    (Dejavu/src/models/modules/block_dejavu.py:575-584, 625-636)."""
+    batch, d = x.shape
+    _require_cuda(x, residual, weight, bias, xbias)
+    assert x.dtype == torch.float16 and weight.dtype == torch.float16 and bias.dtype == torch.float16
+    x = x.contiguous()
+    if residual is not None:
+        assert residual.shape == x.shape and residual.dtype == x.dtype
+        residual = residual.contiguous()
+    y = torch.empty_like(x)
+    r = torch.empty_like(x)
+    call("djv_add_layernorm", y.data_ptr(), r.data_ptr(), x.data_ptr(), _ptr(residual), _ptr(xbias),
+         weight.data_ptr(), bias.data_ptr(), batch, d, float(eps), _stream())
+    return y, r
+
+
+def decode_attention(q, k_cache, v_cache, head_idx, length: int, softmax_scale: float):
+    """ctx[b,h] = softmax(scale * q[b,h] . K[b,h,:length]) V[b,h,:length] for h in head_idx (or all heads
+    when head_idx is None); rows of other heads are uninitialised. q (B, nheads, hd);
+    k_cache (B, nheads, hd/8, S, 8); v_cache (B, nheads, S, hd). Stands in for
+    ft_attention.single_query_attention at Dejavu/src/models/modules/mha_dejavu.py:1439-1446."""
+    B, nheads, hd = q.shape
+    S = v_cache.shape[2]
+    assert v_cache.shape == (B, nheads, S, hd) and k_cache.shape == (B, nheads, hd // 8, S, 8)
+    assert q.dtype == k_cache.dtype == v_cache.dtype == torch.float16
+    assert 0 <= length <= S
+    _require_cuda(q, k_cache, v_cache, head_idx)
+    q = q.contiguous()
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    nnz = nheads
+    if head_idx is not None:
+        assert head_idx.dtype == torch.int32 and head_idx.dim() == 1
+        head_idx = head_idx.contiguous()
+        nnz = head_idx.shape[0]
+    ctx = torch.empty_like(q)
+    need = _lib.load().djv_decode_attn_scratch_bytes(max(nnz, 1), B, hd, S)
+    scratch = _scratch(need, q.device)
+    call("djv_decode_attn", ctx.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _ptr(head_idx),
+         nnz, B, nheads, hd, S, length, float(softmax_scale), scratch.data_ptr(), scratch.numel(), _stream())
+    return ctx

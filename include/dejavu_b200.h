@@ -1,0 +1,235 @@
+/*
+ * dejavu_b200.h — C ABI of the B200 (sm_100a) contextual-sparse decode kernels.
+ *
+ * Every entry point
+ *   - takes raw device pointers, plain sizes and a CUDA stream (as void*; NULL = legacy default stream),
+ *   - only enqueues work on that stream: it never synchronises and never allocates or frees memory
+ *     (scratch is caller-provided) unless its comment says otherwise,
+ *   - returns DJV_OK (0) or a negative DJV_ERR_* code; djv_last_error() then holds a message
+ *     for the calling thread,
+ *   - does NOT validate index *values* on the device (like the kernels it replaces:
+ *     Dejavu/src/ops/triton/gather_gemv.py:70), only shapes, alignment and limits on the host.
+ *
+ * All matrices are row-major fp16 ("half") unless stated. "ld" arguments are row strides in elements.
+ * Citations name the interface in FMInference/DejaVu that each entry point replaces.
+ */
+#ifndef DEJAVU_B200_H
+#define DEJAVU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DJV_OK 0
+#define DJV_ERR_INVALID (-1)     /* bad pointer / shape / alignment / limit            */
+#define DJV_ERR_UNSUPPORTED (-2) /* legal request this build has no kernel for         */
+#define DJV_ERR_CUDA (-3)        /* CUDA runtime reported an error at launch           */
+#define DJV_ERR_SCRATCH (-4)     /* caller-provided scratch too small                  */
+#define DJV_ERR_TIMEOUT (-5)     /* a bounded device-side wait ran out (status word)   */
+
+/* activation codes (Dejavu/src/ops/triton/gather_gemv.py:211) */
+#define DJV_ACT_ID 0
+#define DJV_ACT_RELU 1
+#define DJV_ACT_GELU 2
+#define DJV_ACT_GELU_APPROX 3
+#define DJV_ACT_SQUARED_RELU 4
+
+/* Limits shared with the host-side shims. */
+#define DJV_MAX_BATCH 32        /* rows of x for the GEMV kernels                        */
+#define DJV_KV_WINDOW 16        /* lazy K/V window (Dejavu/src/models/modules/mha_dejavu.py:1243) */
+
+int djv_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+const char *djv_last_error(void);
+const char *djv_status_string(int status);
+/* Number of kernels launched by this library on this process since load (all threads). */
+unsigned long long djv_launch_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Gather GEMV (fc1):  y[b,m] = act( sum_n w[idx[m],n] * x[b,n] + bias[idx[m]] ),  b<B, m<M.
+ * Replaces gather_gemv / gather_gemv_kernel, Dejavu/src/ops/triton/gather_gemv.py:198-254, 23-195.
+ *   y (B,M) fp16 | w (Z,N) rows of stride ldw | x (B,N) | idx (M,) int32 or int64 (idx_is_64), or
+ *   NULL for the identity (dense GEMV over rows 0..M-1) | bias (Z,) or NULL.
+ * Requirements: N % 8 == 0, ldw % 8 == 0, w/x 16-byte aligned, 1 <= B <= DJV_MAX_BATCH.
+ * fp32 accumulation, one rounding to fp16 at the store.
+ * ------------------------------------------------------------------------------------------- */
+int djv_gather_gemv(void *y, const void *w, const void *x, const void *idx, const void *bias,
+                    int B, int N, int M, long long ldw, int idx_is_64, int act, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Gather transposed GEMV (fc2):  y[b,n] = sum_m w[idx[m],n] * x[b,m] + bias[n].
+ * Replaces gather_transposed_gemv, Dejavu/src/ops/triton/gather_gemv.py:572-644 (both its
+ * atomic-add and its deterministic kernel, :432-569 and :263-425). Deterministic: partial sums over
+ * fixed row chunks are written to scratch and combined in a fixed order by the last block to finish.
+ *   y (B,N) fp16 | w (Z,N) stride ldw = W2 transposed | x (B,M) | idx (M,) or NULL | bias (N,) or NULL.
+ *   scratch: at least djv_gather_transposed_gemv_scratch_bytes(B,N,M) bytes, 256-byte aligned, and its
+ *   first 4096 bytes must be ZERO before the first call (the kernel leaves them zero again).
+ *   Calls that share scratch must not overlap on the GPU.
+ * ------------------------------------------------------------------------------------------- */
+size_t djv_gather_transposed_gemv_scratch_bytes(int B, int N, int M);
+int djv_gather_transposed_gemv(void *y, const void *w, const void *x, const void *idx,
+                               const void *bias, int B, int N, int M, long long ldw, int idx_is_64,
+                               void *scratch, size_t scratch_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sparse MLP in one call: y = gather_transposed_gemv(relu(gather_gemv(x,W1,idx,b1)), W2t, idx, b2).
+ * Replaces mlp_sparse, Dejavu/src/ops/triton/gather_gemv.py:647-657. h is rounded to fp16 between
+ * the two products exactly as there (:233). h (B,M) fp16 is caller-provided workspace.
+ * ------------------------------------------------------------------------------------------- */
+int djv_mlp_sparse(void *y, void *h, const void *w1, const void *w2t, const void *x, const void *idx,
+                   const void *bias1, const void *bias2, int B, int N, int M, long long ldw1,
+                   long long ldw2t, int idx_is_64, void *scratch, size_t scratch_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Top-K index selection over one score vector.
+ * Replaces mlp_sp_logit.topk(K, sorted=False) / att_sp_logit.topk(K) + .to(int32),
+ * Dejavu/src/models/modules/mha_dejavu.py:1069, 1369, 1506-1507.
+ * Rule: the K largest scores; ties on the K-th score go to the LOWEST indices; NaN ranks above +inf.
+ * Output: K indices in ascending index order, written as int32 to idx32 and/or int64 to idx64
+ * (either may be NULL). scores: fp16 (score_is_f32 = 0) or fp32. 0 <= K <= n, n*elemsize <= 200 KiB.
+ * ------------------------------------------------------------------------------------------- */
+int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int n, int K, int score_is_f32,
+             void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Head-sparse QKV projection with the reference's operator semantics:
+ *   y[t,q,h,:] = x[t,:] . w[q,h,:,:]^T + bias[q,h,:]  for h in head_idx and token rows t with
+ *   batch_idx[i,t] >= 0 (i = position of h in head_idx); other entries of y are left untouched.
+ * Replaces qkv_proj_sparse, Dejavu/src/ops/triton/attention_proj_sparse.py:110-194.
+ *   y (T,3,nheads,hd) | w (3,nheads,hd,d) contiguous | x (T,d), T <= 16 | head_idx (nnz,) int32 |
+ *   batch_idx (nnz,T) int32 | bias (3,nheads,hd) or NULL. hd in {32,64,128}, d % 8 == 0.
+ * ------------------------------------------------------------------------------------------- */
+int djv_qkv_proj_sparse(void *y, const void *w, const void *x, const int32_t *head_idx,
+                        const int32_t *batch_idx, const void *bias, int T, int d, int nheads, int hd,
+                        int nnz, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Head-sparse output projection: y[b,n] = sum_{h in head_idx} x[b,h,:] . w[n,h,:] + bias[n].
+ * Replaces out_proj_sparse, Dejavu/src/ops/triton/attention_proj_sparse.py:274-338.
+ *   y (B,d) | w (d,nheads,hd) contiguous (= out_proj.weight viewed per head) | x (B,nheads,hd) |
+ *   head_idx (nnz,) int32 | bias (d,) or NULL. B <= 16.
+ * n_active_dev: optional device int32; when non-NULL only the first *n_active_dev entries of head_idx
+ * are used (nnz is then the capacity of head_idx).
+ * ------------------------------------------------------------------------------------------- */
+int djv_out_proj_sparse(void *y, const void *w, const void *x, const int32_t *head_idx,
+                        const int32_t *n_active_dev, const void *bias, int B, int d, int nheads, int hd,
+                        int nnz, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Scatter recomputed K / V rows of selected heads into the decode caches.
+ * Replace k_cache_copy_sparse / v_cache_copy_sparse,
+ * Dejavu/src/ops/triton/attention_proj_sparse.py:525-590, 396-456.
+ *   k, v (T,nheads,hd) (may be strided views: row stride ld_t, head stride ld_h, in elements)
+ *   k_cache (1,nheads,hd/8,S,8)   v_cache (1,nheads,S,hd)
+ *   head_idx (nnz,) int32 | seqlen_idx (nnz,T) int32, negative = skip |
+ *   padding: device int32 added to every destination position, or NULL (= 0).
+ * ------------------------------------------------------------------------------------------- */
+int djv_k_cache_copy_sparse(const void *k, void *k_cache, const int32_t *head_idx,
+                            const int32_t *seqlen_idx, const int32_t *padding, int T, int nheads,
+                            int hd, int S, int nnz, long long ld_t, long long ld_h, void *stream);
+int djv_v_cache_copy_sparse(const void *v, void *v_cache, const int32_t *head_idx,
+                            const int32_t *seqlen_idx, const int32_t *padding, int T, int nheads,
+                            int hd, int S, int nnz, long long ld_t, long long ld_h, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Lazy-K/V decode state of one attention layer, kept on the device so that a captured CUDA graph
+ * replays correctly. Replaces ParallelTracker + x_cache + counter + cache_offset,
+ * Dejavu/src/models/modules/mha_dejavu.py:1124-1149, 1243-1253, 1318-1329, 1355-1359, 1485-1492.
+ *
+ * struct layout (int32 words) of `state`, DJV_ATTN_STATE_WORDS + nheads words in total:
+ *   [0] slot      position of the current token inside the 16-token window (0..15)
+ *   [1] base      cache position of window slot 0
+ *   [2] n_eff     number of heads in use this step (after the every-16th-step flush rule)
+ *   [3] status    0, or DJV_ERR_* written by a kernel that found the state inconsistent
+ *   [4..7] reserved
+ *   [8 .. 8+nheads)          pending[h]: bit s set = head h has no K,V yet for window slot s
+ *   [8+nheads .. 8+2*nheads) eff_heads[i], i < n_eff: heads in use this step
+ *   [8+2*nheads .. 8+3*nheads) rowmask[i]: window slots whose K,V this step computes for eff_heads[i]
+ * ------------------------------------------------------------------------------------------- */
+#define DJV_ATTN_STATE_HDR 8
+#define DJV_ATTN_STATE_WORDS(nheads) (DJV_ATTN_STATE_HDR + 3 * (nheads))
+
+/* state := {slot 0, base = prompt_len, nothing pending}. */
+int djv_attn_state_reset(int32_t *state, int nheads, int prompt_len, void *stream);
+
+/* One decode step of the head-sparse attention block for batch 1 (mha_dejavu.py:1312-1359, 1422-1446):
+ *   1. x_ring[slot] = x; choose the heads in use: head_idx[0..nnz) (device int32), or ALL heads when
+ *      slot == 15 (flush rule, :1320-1325) or when head_idx == NULL (dense step);
+ *   2. for each head in use: K,V for every window slot it still lacks (plus the current one) are
+ *      projected from x_ring and written straight into the caches at base+slot; q of the current
+ *      token goes to q_out (nheads,hd); heads not in use get the current slot marked pending;
+ *   3. single-query softmax attention over cache positions [0, base+slot] for the heads in use,
+ *      scale = softmax_scale, context written to ctx (nheads,hd) (rows of unused heads untouched);
+ *   4. advance: slot+1, and after slot 15: slot = 0, base += 16.
+ * Step 4 happens in djv_attn_step_finish so that djv_out_proj_sparse can still read eff_heads/n_eff.
+ *   wqkv (3,nheads,hd,d) | bqkv (3,nheads,hd) or NULL | x (d,) | x_ring (16,d) |
+ *   k_cache (1,nheads,hd/8,S,8) | v_cache (1,nheads,S,hd) | scratch >= djv_attn_step_scratch_bytes().
+ * ------------------------------------------------------------------------------------------- */
+size_t djv_attn_step_scratch_bytes(int nheads, int hd, int S);
+int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, const void *x,
+                  void *x_ring, void *k_cache, void *v_cache, int32_t *state,
+                  const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
+                  float softmax_scale, void *scratch, size_t scratch_bytes, void *stream);
+int djv_attn_step_finish(int32_t *state, int nheads, void *stream);
+
+/* Single-query attention over the caches for an explicit head list (no lazy state):
+ *   ctx[b,h,:] = softmax(scale * q[b,h,:] . K[b,h,0..len))) V[b,h,0..len)  for h in head_idx
+ * Replaces the call ft_attention.single_query_attention(...), mha_dejavu.py:1439-1446 (third-party
+ * kernel, flash-attention v0.2.8 csrc/ft_attention) restricted to the heads that are read afterwards.
+ *   q, ctx (B,nheads,hd) | k_cache (B,nheads,hd/8,S,8) | v_cache (B,nheads,S,hd) |
+ *   head_idx (nnz,) int32 or NULL = all heads | len = number of cached positions to attend to.
+ * ------------------------------------------------------------------------------------------- */
+size_t djv_decode_attn_scratch_bytes(int nnz, int B, int hd, int S);
+int djv_decode_attn(void *ctx, const void *q, const void *k_cache, const void *v_cache,
+                    const int32_t *head_idx, int nnz, int B, int nheads, int hd, int S, int len,
+                    float softmax_scale, void *scratch, size_t scratch_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Residual add + LayerNorm:  r = x + residual (+ xbias);  y = LN(r) * gamma + beta.
+ * Replaces the un-fused `residual = dropped + residual; hidden = norm(residual)`,
+ * Dejavu/src/models/modules/block_dejavu.py:575-584, 625-636. r is rounded to fp16 before the
+ * statistics are taken, as the reference's fp16 add does.
+ *   x, residual, r_out, y (B,d) | xbias (d,) or NULL | residual may be NULL (r = x) |
+ *   r_out may alias residual.
+ * ------------------------------------------------------------------------------------------- */
+int djv_add_layernorm(void *y, void *r_out, const void *x, const void *residual, const void *xbias,
+                      const void *gamma, const void *beta, int B, int d, float eps, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Tensor-parallel one-shot all-reduce fused with the residual add and LayerNorm that follow it:
+ *   r = sum_ranks(partial) + residual;  y = LN(r)
+ * Replaces all_reduce(out, process_group) at mha_dejavu.py:1498 and
+ * Dejavu/src/ops/fused_dense_sparse_dejavu.py:937-940 together with the add + norm of
+ * block_dejavu.py:575-584, 625-636. Every rank sums the peers' partials in rank order (deterministic,
+ * identical on all ranks) with plain loads over NVLink; waits on peers are bounded and report
+ * DJV_ERR_TIMEOUT through comm->status instead of hanging.
+ *
+ * djv_comm is created per process from peer-mapped buffers the host exchanged (CUDA IPC):
+ *   bufs[r]  : rank r's exchange buffer, `slots` slots of slot_bytes each, mapped into this process
+ *   flags[r] : rank r's flag array (world*slots uint32), mapped into this process
+ * ------------------------------------------------------------------------------------------- */
+typedef struct djv_comm djv_comm;
+/* Set-up helpers (these DO allocate / free with cudaMalloc / cudaFree and zero the memory): a buffer
+ * that is the base of its own allocation, as CUDA IPC handles require. */
+int djv_ipc_alloc(size_t bytes, void **dev_ptr_out);
+int djv_ipc_free(void *dev_ptr);
+int djv_ipc_get_handle(const void *dev_ptr, unsigned char handle_out[64]);
+int djv_ipc_open(const unsigned char handle[64], void **dev_ptr_out);
+int djv_ipc_close(void *dev_ptr);
+int djv_comm_create(djv_comm **out, int rank, int world, void *const *bufs, void *const *flags,
+                    size_t slot_bytes, int slots);
+int djv_comm_destroy(djv_comm *comm);
+/* Reads the device status word (synchronises the stream the comm last ran on). */
+int djv_comm_status(djv_comm *comm);
+/* partial: this rank's (B,d) fp16 partial sums. B*d*2 <= slot_bytes. */
+int djv_allreduce_add_layernorm(djv_comm *comm, void *y, void *r_out, const void *partial,
+                                const void *residual, const void *gamma, const void *beta, int B,
+                                int d, float eps, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEJAVU_B200_H */
