@@ -599,7 +599,7 @@ static int launch_out_proj(int B, __half *Y, const __half *W, const __half *X, c
 extern "C" int djv_out_proj_sparse(void *y, const void *w, const void *x, const int32_t *head_idx,
                                    const int32_t *n_active_dev, const void *bias, int B, int d,
                                    int nheads, int hd, int nnz, void *stream) {
-  DJV_REQUIRE(y && w && x && head_idx, "out_proj_sparse: null pointer");
+  DJV_REQUIRE(y && w && x && (head_idx || nnz == 0), "out_proj_sparse: null pointer");
   int rc = check_hd("out_proj_sparse", hd, d);
   if (rc) return rc;
   DJV_REQUIRE(B >= 1 && B <= 16, "out_proj_sparse: batch %d outside [1,16]", B);

@@ -95,3 +95,12 @@ __device__ __forceinline__ float apply_act(float v) {
 }
 
 }  // namespace djv
+
+namespace djv {
+// idx == nullptr means the identity index list
+__device__ __forceinline__ long long load_index(const void *idx, int m, int idx64) {
+  if (idx == nullptr) return m;
+  return idx64 ? reinterpret_cast<const long long *>(idx)[m]
+               : static_cast<long long>(reinterpret_cast<const int *>(idx)[m]);
+}
+}  // namespace djv

@@ -10,14 +10,10 @@
 //   rowdot  : M*N*2 + M*2 (bias) + M*4 (idx) + B*N*2 (x) + B*M*2 (y)
 //   rowaxpy : M*N*2 + B*M*2 (x) + N*2 (bias) + B*N*2 (y)
 #include "common.cuh"
+#include "rowaxpy.cuh"
 
 namespace djv {
 
-__device__ __forceinline__ long long load_index(const void *idx, int m, int idx64) {
-  if (idx == nullptr) return m;
-  return idx64 ? reinterpret_cast<const long long *>(idx)[m]
-               : static_cast<long long>(reinterpret_cast<const int *>(idx)[m]);
-}
 
 // -------------------------------------------------------------------------------------------
 // rowdot. A block has 8 warps split into 8/WPR groups of WPR warps; a group owns ROWS rows at a
@@ -205,197 +201,6 @@ static int rowdot_slice(int B, int act, __half *Y, const __half *W, const __half
   }
   set_error("gather_gemv: internal batch slice %d", B);
   return DJV_ERR_INVALID;
-}
-
-// -------------------------------------------------------------------------------------------
-// rowaxpy. grid = (column tiles, row chunks). A block owns 128*8 = 1024 consecutive columns (one
-// 16-byte chunk per thread) and a contiguous chunk of the index list; it keeps 8*B fp32 sums per
-// thread, writes them to `partial`, and the last block to arrive for a column tile adds the partials
-// in chunk order (deterministic), adds the bias and stores fp16.
-// -------------------------------------------------------------------------------------------
-constexpr int RA_THREADS = 128;
-constexpr int RA_TILE = RA_THREADS * 8;
-constexpr int RA_MAX_RPC = 512;  // rows per chunk held in shared memory
-constexpr int RA_COUNTER_BYTES = 4096;
-
-__device__ __forceinline__ float4 ld_cg_f4(const float *p) {
-  float4 v;
-  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p));
-  return v;
-}
-
-template <int B>
-__global__ void __launch_bounds__(RA_THREADS)
-rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
-               const void *__restrict__ idx, const __half *__restrict__ bias,
-               float *__restrict__ partial, unsigned *__restrict__ counters, int M, int N,
-               long long ldw, int idx64, int rpc) {
-  __shared__ long long offs[RA_MAX_RPC];
-  __shared__ float xs[B][RA_MAX_RPC];
-  __shared__ int is_last;
-
-  const int tid = threadIdx.x;
-  const int tile = blockIdx.x, mc = blockIdx.y, MC = gridDim.y;
-  const int nchunks = N / 8;
-  const int chunk = tile * RA_THREADS + tid;
-  const bool active = chunk < nchunks;
-  const int m_begin = mc * rpc;
-  const int cnt = min(rpc, M - m_begin);
-
-  for (int i = tid; i < cnt; i += RA_THREADS) {
-    offs[i] = load_index(idx, m_begin + i, idx64) * ldw;
-#pragma unroll
-    for (int b = 0; b < B; ++b) xs[b][i] = __half2float(X[(size_t)b * M + m_begin + i]);
-  }
-  __syncthreads();
-
-  float acc[B][8];
-#pragma unroll
-  for (int b = 0; b < B; ++b)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[b][e] = 0.f;
-
-  constexpr int U = 8;
-  if (active) {
-    const __half *wcol = W + (size_t)chunk * 8;
-    for (int i0 = 0; i0 < cnt; i0 += U) {
-      uint4 wv[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (i0 + u < cnt)
-          wv[u] = ld_stream16(wcol + offs[i0 + u]);
-        else
-          wv[u] = make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (i0 + u < cnt) {
-          const float2 w0 = h2f(wv[u].x), w1 = h2f(wv[u].y), w2 = h2f(wv[u].z), w3 = h2f(wv[u].w);
-#pragma unroll
-          for (int b = 0; b < B; ++b) {
-            const float xb = xs[b][i0 + u];
-            acc[b][0] = fmaf(xb, w0.x, acc[b][0]);
-            acc[b][1] = fmaf(xb, w0.y, acc[b][1]);
-            acc[b][2] = fmaf(xb, w1.x, acc[b][2]);
-            acc[b][3] = fmaf(xb, w1.y, acc[b][3]);
-            acc[b][4] = fmaf(xb, w2.x, acc[b][4]);
-            acc[b][5] = fmaf(xb, w2.y, acc[b][5]);
-            acc[b][6] = fmaf(xb, w3.x, acc[b][6]);
-            acc[b][7] = fmaf(xb, w3.y, acc[b][7]);
-          }
-        }
-      }
-    }
-  }
-
-  if (MC > 1) {
-    if (active) {
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        float *p = partial + ((size_t)mc * B + b) * N + (size_t)chunk * 8;
-        __stcg(reinterpret_cast<float4 *>(p), make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]));
-        __stcg(reinterpret_cast<float4 *>(p) + 1,
-               make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]));
-      }
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned ticket = atomicAdd(&counters[tile], 1u);
-      is_last = (ticket == (unsigned)MC - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    if (active) {
-#pragma unroll
-      for (int b = 0; b < B; ++b)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[b][e] = 0.f;
-      for (int c = 0; c < MC; ++c) {
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-          const float *p = partial + ((size_t)c * B + b) * N + (size_t)chunk * 8;
-          const float4 lo = ld_cg_f4(p), hi = ld_cg_f4(p + 4);
-          acc[b][0] += lo.x; acc[b][1] += lo.y; acc[b][2] += lo.z; acc[b][3] += lo.w;
-          acc[b][4] += hi.x; acc[b][5] += hi.y; acc[b][6] += hi.z; acc[b][7] += hi.w;
-        }
-      }
-    }
-    if (tid == 0) counters[tile] = 0;  // ready for the next launch
-  }
-
-  if (active) {
-    float bz[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) bz[e] = 0.f;
-    if (bias != nullptr) {
-      const uint4 bvv = ld_cached16(bias + (size_t)chunk * 8);
-      const float2 b0 = h2f(bvv.x), b1 = h2f(bvv.y), b2 = h2f(bvv.z), b3 = h2f(bvv.w);
-      bz[0] = b0.x; bz[1] = b0.y; bz[2] = b1.x; bz[3] = b1.y;
-      bz[4] = b2.x; bz[5] = b2.y; bz[6] = b3.x; bz[7] = b3.y;
-    }
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      __half2 o[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        o[e] = __floats2half2_rn(acc[b][2 * e] + bz[2 * e], acc[b][2 * e + 1] + bz[2 * e + 1]);
-      *reinterpret_cast<uint4 *>(Y + (size_t)b * N + (size_t)chunk * 8) =
-          *reinterpret_cast<uint4 *>(o);
-    }
-  }
-}
-
-struct RowaxpyPlan {
-  int tiles, mc, rpc;
-};
-
-static RowaxpyPlan plan_rowaxpy(int M, int N) {
-  const int sms = sm_count();
-  const int tiles = ceil_div(N / 8, RA_THREADS);
-  int mc = ceil_div(sms * 6, tiles);          // ~6 blocks of 128 threads per SM
-  const int min_rows = 8;                     // at least one full unroll of rows per block
-  if (mc > ceil_div(M, min_rows)) mc = ceil_div(M, min_rows);
-  if (mc < 1) mc = 1;
-  int rpc = ceil_div(M, mc);
-  if (rpc > RA_MAX_RPC) rpc = RA_MAX_RPC;
-  if (rpc < 1) rpc = 1;
-  mc = ceil_div(M, rpc);
-  if (mc < 1) mc = 1;
-  return {tiles, mc, rpc};
-}
-
-static size_t rowaxpy_scratch_bytes(int B, int N, int M) {
-  const RowaxpyPlan p = plan_rowaxpy(M, N);
-  return RA_COUNTER_BYTES + (size_t)p.mc * B * N * sizeof(float);
-}
-
-template <int B>
-static void launch_rowaxpy(const RowaxpyPlan &p, __half *Y, const __half *W, const __half *X,
-                           const void *idx, const __half *bias, float *partial, unsigned *counters,
-                           int M, int N, long long ldw, int idx64, cudaStream_t st) {
-  dim3 grid(p.tiles, p.mc);
-  rowaxpy_kernel<B><<<grid, RA_THREADS, 0, st>>>(Y, W, X, idx, bias, partial, counters, M, N, ldw,
-                                                 idx64, p.rpc);
-}
-
-static int rowaxpy_slice(int B, __half *Y, const __half *W, const __half *X, const void *idx,
-                         const __half *bias, void *scratch, int M, int N, long long ldw, int idx64,
-                         cudaStream_t st) {
-  const RowaxpyPlan p = plan_rowaxpy(M, N);
-  unsigned *counters = reinterpret_cast<unsigned *>(scratch);
-  float *partial = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + RA_COUNTER_BYTES);
-  switch (B) {
-    case 1: launch_rowaxpy<1>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
-    case 2: launch_rowaxpy<2>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
-    case 3: launch_rowaxpy<3>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
-    case 4: launch_rowaxpy<4>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
-    default: set_error("gather_transposed_gemv: internal batch slice %d", B); return DJV_ERR_INVALID;
-  }
-  return DJV_OK;
 }
 
 // Zero rows selected (M == 0): y = bias (or 0).

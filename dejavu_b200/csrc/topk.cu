@@ -176,6 +176,7 @@ extern "C" int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int 
   DJV_REQUIRE(scores != nullptr, "topk: null scores");
   DJV_REQUIRE(n >= 1, "topk: n=%d", n);
   DJV_REQUIRE(K >= 0 && K <= n, "topk: K=%d outside [0,%d]", K, n);
+  if (K == 0) return DJV_OK;
   DJV_REQUIRE(idx32 || idx64, "topk: no output pointer");
   const size_t bytes = (size_t)n * (score_is_f32 ? 4 : 2);
   if (bytes > 200 * 1024) {

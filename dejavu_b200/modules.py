@@ -1,0 +1,441 @@
+"""Host-side mirror of the reference's sparse decode modules, same class names, constructor arguments,
+forward signatures and state-dict keys, running the sm_100a kernels for the decode step.
+
+  ParallelSP, ColumnParallelLinear, RowParallelLinear, RowParallelLinearNoReduce, ParallelFusedMLPDejavu
+      <- Dejavu/src/ops/fused_dense_sparse_dejavu.py:33-76, 241-317, 783-818, 821-951
+  ParallelMHASparseAttMlp, ParallelMHADejavu
+      <- Dejavu/src/models/modules/mha_dejavu.py:1152-1511, 910-1075
+  BlockMlpAttSparse, BlockDejavu
+      <- Dejavu/src/models/modules/block_dejavu.py:464-663, 264-461
+
+Differences that are deliberate (none changes results for heads / neurons that are read):
+  * the lazy-K/V bookkeeping (ParallelTracker, x_cache, counter, cache_offset) lives in device memory, so
+    a captured CUDA graph replays correctly;
+  * decode attention runs only for the heads in use (the reference runs all local heads and discards
+    the others);
+  * fc2's weight is stored once, transposed (ffn_local, d); `fc2.weight` is a (d, ffn_local) view of it,
+    so nothing is duplicated or built lazily inside forward;
+  * the predictor look-ahead work runs on the same stream as the rest of the step (the whole step is
+    one CUDA graph); the reference's side stream is an overlap device, not a semantic one.
+The prompt phase (seqlen > 1) is dense and uses torch (cuBLAS / SDPA), as in the reference.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib, ops
+from ._lib import call
+
+KV_WINDOW = _lib.KV_WINDOW
+
+
+def _world(pg) -> int:
+    return 1 if pg is None else pg.size()
+
+
+def _rank(pg) -> int:
+    return 0 if pg is None else pg.rank()
+
+
+def all_reduce(x: torch.Tensor, process_group) -> torch.Tensor:
+    """SUM over the tensor-parallel group (flash_attn.utils.distributed.all_reduce at
+    Dejavu/src/models/modules/mha_dejavu.py:1498, fused_dense_sparse_dejavu.py:940)."""
+    if _world(process_group) == 1:
+        return x
+    x = x.contiguous()
+    torch.distributed.all_reduce(x, group=process_group)
+    return x
+
+
+class ColumnParallelLinear(nn.Module):
+    """Linear whose OUTPUT features are split over the group: weight (out/world, in)
+    (fused_dense_sparse_dejavu.py:241-277)."""
+
+    def __init__(self, in_features, out_features, process_group, bias=True, sequence_parallel=False,
+                 device=None, dtype=None):
+        super().__init__()
+        world = _world(process_group)
+        if out_features % world != 0:
+            raise ValueError(f"out_features ({out_features}) must be divisible by world_size ({world})")
+        self.process_group = process_group
+        self.in_features, self.out_features = in_features, out_features // world
+        self.weight = nn.Parameter(torch.empty(self.out_features, in_features, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.empty(self.out_features, device=device, dtype=dtype)) if bias else None
+
+    def forward(self, x):
+        return F.linear(x, self.weight, self.bias)
+
+
+class RowParallelLinearNoReduce(nn.Module):
+    """Linear whose INPUT features are split over the group: weight (out, in/world); bias on rank 0 only;
+    the caller all-reduces (fused_dense_sparse_dejavu.py:783-818)."""
+
+    def __init__(self, in_features, out_features, process_group, bias=True, sequence_parallel=False,
+                 device=None, dtype=None):
+        super().__init__()
+        world = _world(process_group)
+        if in_features % world != 0:
+            raise ValueError(f"in_features ({in_features}) must be divisible by world_size ({world})")
+        self.process_group = process_group
+        self.in_features, self.out_features = in_features // world, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, self.in_features, device=device, dtype=dtype))
+        has_bias = bias and _rank(process_group) == 0
+        self.bias = nn.Parameter(torch.empty(out_features, device=device, dtype=dtype)) if has_bias else None
+
+    def forward(self, x):
+        return F.linear(x, self.weight, self.bias)
+
+
+class RowParallelLinear(RowParallelLinearNoReduce):
+    """Same, followed by the all-reduce (fused_dense_sparse_dejavu.py:280-317)."""
+
+    def forward(self, x):
+        return all_reduce(F.linear(x, self.weight, self.bias), self.process_group)
+
+
+class _TransposedRowParallelLinear(RowParallelLinear):
+    """fc2 of the sparse MLP: storage is the transposed weight (in/world, out), contiguous, which is what
+    the gather kernel streams; `.weight` is the usual (out, in/world) view of the same memory."""
+
+    def __init__(self, in_features, out_features, process_group, bias=True, sequence_parallel=False,
+                 device=None, dtype=None):
+        nn.Module.__init__(self)
+        world = _world(process_group)
+        if in_features % world != 0:
+            raise ValueError(f"in_features ({in_features}) must be divisible by world_size ({world})")
+        self.process_group = process_group
+        self.in_features, self.out_features = in_features // world, out_features
+        storage = torch.empty(self.in_features, out_features, device=device, dtype=dtype)
+        self.weight = nn.Parameter(storage.t())
+        has_bias = bias and _rank(process_group) == 0
+        self.bias = nn.Parameter(torch.empty(out_features, device=device, dtype=dtype)) if has_bias else None
+
+    @property
+    def weight_t(self) -> torch.Tensor:
+        return self.weight.t()  # contiguous (in/world, out)
+
+
+class ParallelSP(nn.Module):
+    """Low-rank sparsity predictor: fc1(fc0(x)), both bias-free; fc0 replicated, fc1 split by output;
+    K is the PER-RANK budget K // world (fused_dense_sparse_dejavu.py:33-76, mha_dejavu.py:1078-1121)."""
+
+    def __init__(self, layer_idx=None, embed_dim=None, low_rank_dim=None, out_dim=None, K=None,
+                 process_group=None, sequence_parallel=False, device=None, dtype=None) -> None:
+        super().__init__()
+        assert process_group is not None, "sparse predictor only implemented with parallel for now"
+        self.process_group = process_group
+        self.layer_idx = layer_idx
+        self.embed_dim = embed_dim
+        self.fc0 = nn.Linear(embed_dim, low_rank_dim, bias=False, device=device, dtype=dtype)
+        self.out = out_dim // _world(process_group)
+        self.fc1 = ColumnParallelLinear(low_rank_dim, out_dim, process_group, bias=False,
+                                        sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+        self.K = K // _world(process_group)
+
+    def forward(self, x):
+        x = ops.dense_gemv(x.view(1, self.embed_dim), self.fc0.weight)  # 1 x low_rank
+        x = ops.dense_gemv(x, self.fc1.weight)
+        return x.view(-1)
+
+
+class ParallelFusedMLPDejavu(nn.Module):
+    """MLP with contextual sparsity: forward(x, residual, idx) -> (out, mlp_logit). With idx (decode) only
+    the rows idx of fc1 / fc2^T are read; mlp_logit = sp(residual) selects the NEXT layer's neurons
+    (fused_dense_sparse_dejavu.py:821-951)."""
+
+    has_predictor = True
+
+    def __init__(self, in_features, hidden_features, sp_kwargs, out_features=None, activation="gelu_approx",
+                 layer_idx=None, process_group=None, bias1=True, bias2=True, sequence_parallel=True,
+                 checkpoint_lvl=0, heuristic="auto", device=None, dtype=None):
+        assert checkpoint_lvl in [0, 1, 2]
+        assert activation in ["gelu_approx", "relu"]
+        assert process_group is not None
+        assert sp_kwargs is not None or not self.has_predictor, "sparse predictor parameters are not passed in."
+        super().__init__()
+        if out_features is None:
+            out_features = in_features
+        factory = {"device": device, "dtype": dtype}
+        self.activation = activation
+        self.process_group = process_group
+        self.sequence_parallel = sequence_parallel
+        self.layer_idx = layer_idx
+        self.fc1 = ColumnParallelLinear(in_features, hidden_features, process_group, bias=bias1, **factory)
+        self.fc2 = _TransposedRowParallelLinear(hidden_features, out_features, process_group, bias=bias2, **factory)
+        if self.has_predictor:
+            self.sp = ParallelSP(layer_idx=layer_idx, device=device, dtype=dtype, process_group=process_group,
+                                 sequence_parallel=sequence_parallel, **sp_kwargs)
+        self.skip_all_reduce = False  # set by the block when it fuses the all-reduce with add+LN
+
+    @property
+    def fc2_weight_t(self):
+        return self.fc2.weight_t
+
+    def forward(self, x, residual, idx=None):
+        do_token_generation = x.size(1) == 1
+        if idx is not None:
+            assert x.size(1) == 1
+            assert self.activation == "relu", "the sparse path applies ReLU (gather_gemv.py:655)"
+            out = ops.mlp_sparse(x.view(x.size(0), -1), self.fc1.weight, self.fc2.weight_t, idx, self.fc1.bias,
+                                 self.fc2.bias)
+            out = out.view(x.size(0), 1, -1)
+        elif do_token_generation:
+            act = "relu" if self.activation == "relu" else "gelu_approx"
+            h = ops.dense_gemv(x.view(x.size(0), -1), self.fc1.weight, self.fc1.bias, act)
+            out = ops.dense_transposed_gemv(h, self.fc2.weight_t, self.fc2.bias).view(x.size(0), 1, -1)
+        else:
+            h = F.linear(x, self.fc1.weight, self.fc1.bias)
+            h = F.relu(h) if self.activation == "relu" else F.gelu(h, approximate="tanh")
+            out = F.linear(h, self.fc2.weight, self.fc2.bias)
+        if not self.skip_all_reduce:
+            out = all_reduce(out, self.process_group)
+        mlp_logit = self.sp(residual) if (do_token_generation and self.has_predictor) else None
+        return out, mlp_logit
+
+
+class ParallelFusedMLP(ParallelFusedMLPDejavu):
+    """The dense MLP of the comparator model (fused_dense_sparse_dejavu.py:696-780): no predictor; decode
+    GEMVs go through cuBLAS (torch), which is the dense fp16 decode the sparse path is measured against."""
+
+    has_predictor = False
+
+    def __init__(self, in_features, hidden_features, out_features=None, activation="gelu_approx", layer_idx=None,
+                 process_group=None, bias1=True, bias2=True, sequence_parallel=True, checkpoint_lvl=0,
+                 heuristic="auto", device=None, dtype=None):
+        super().__init__(in_features, hidden_features, None, out_features=out_features, activation=activation,
+                         layer_idx=layer_idx, process_group=process_group, bias1=bias1, bias2=bias2,
+                         sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+
+    def forward(self, x, residual=None, idx=None):
+        h = F.linear(x, self.fc1.weight, self.fc1.bias)
+        h = F.relu(h) if self.activation == "relu" else F.gelu(h, approximate="tanh")
+        out = F.linear(h, self.fc2.weight, self.fc2.bias)
+        if not self.skip_all_reduce:
+            out = all_reduce(out, self.process_group)
+        return out, None
+
+
+class ParallelMHASparseAttMlp(nn.Module):
+    """Self-attention with head sparsity in decode. forward(x, residual, head_idx, mlp_sp_logit, seqlen,
+    inference_params) -> (out, mlp_idx, att_idx): mlp_idx = top-mlp_k of mlp_sp_logit for THIS layer's MLP,
+    att_idx = top-att_k of sp(residual) for the NEXT layer's attention (mha_dejavu.py:1152-1511)."""
+
+    sparse_attention = True
+
+    def __init__(self, embed_dim, num_heads, process_group, sp_kwargs, bias=True, dropout=0.0,
+                 softmax_scale=None, causal=False, layer_idx=None, rotary_emb_dim=0, rotary_emb_scale_base=0,
+                 use_flash_attn=False, checkpointing=False, sequence_parallel=True, device=None,
+                 dtype=None) -> None:
+        super().__init__()
+        assert rotary_emb_dim == 0, "OPT uses learned positions; rotary embeddings are not on this path"
+        self.embed_dim = embed_dim
+        self.causal = causal
+        self.layer_idx = layer_idx
+        self.process_group = process_group
+        self.num_heads = num_heads
+        assert embed_dim % num_heads == 0, "embed_dim must be divisible by num_heads"
+        self.head_dim = embed_dim // num_heads
+        world = _world(process_group)
+        assert num_heads % world == 0
+        self.num_head_per_node = num_heads // world
+        self.softmax_scale = softmax_scale if softmax_scale is not None else self.head_dim ** -0.5
+        factory = {"device": device, "dtype": dtype}
+        self.Wqkv = ColumnParallelLinear(embed_dim, 3 * embed_dim, process_group, bias=bias,
+                                         sequence_parallel=sequence_parallel, **factory)
+        self.out_proj = RowParallelLinearNoReduce(embed_dim, embed_dim, process_group, bias=bias,
+                                                  sequence_parallel=sequence_parallel, **factory)
+        self.sp = None
+        if self.sparse_attention:
+            self.sp = ParallelSP(layer_idx=layer_idx, device=device, dtype=dtype, process_group=process_group,
+                                 sequence_parallel=sequence_parallel, **sp_kwargs)
+        self.mlp_k = None  # per-rank budgets, copied in by the block (block_dejavu.py:549-553)
+        self.att_k = None
+        self.skip_all_reduce = False
+        self._bufs = None
+
+    # ---- device-resident decode state --------------------------------------------------------
+    def _decode_buffers(self, device, S):
+        n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
+        if self._bufs is None or self._bufs["S"] != S or self._bufs["state"].device != device:
+            need = _lib.load().djv_attn_step_scratch_bytes(n, hd, S)
+            self._bufs = {
+                "S": S,
+                "state": torch.zeros(_lib.ATTN_STATE_HDR + 3 * n, dtype=torch.int32, device=device),
+                "x_ring": torch.zeros(KV_WINDOW, d, dtype=torch.float16, device=device),
+                "q": torch.zeros(n, hd, dtype=torch.float16, device=device),
+                "ctx": torch.zeros(1, n, hd, dtype=torch.float16, device=device),
+                "scratch": torch.zeros(max(need, 4096), dtype=torch.uint8, device=device),
+            }
+        return self._bufs
+
+    def reset_decode_state(self, prompt_len: int, device, S: int):
+        b = self._decode_buffers(device, S)
+        call("djv_attn_state_reset", b["state"].data_ptr(), self.num_head_per_node, int(prompt_len), ops._stream())
+
+    def decode_status(self) -> int:
+        """0, or the negative status a kernel left in the state (synchronises)."""
+        return 0 if self._bufs is None else int(self._bufs["state"][3].item())
+
+    # ---- prompt phase: dense ------------------------------------------------------------------
+    def _prompt_attention(self, x, inference_params):
+        B, L, _ = x.shape
+        n, hd = self.num_head_per_node, self.head_dim
+        qkv = self.Wqkv(x).view(B, L, 3, n, hd)
+        q, k, v = qkv.unbind(2)
+        if inference_params is not None:
+            assert B == 1, "the sparse decode path keeps one sequence (mha_dejavu.py:1318, 1469)"
+            k_cache, v_cache = inference_params.key_value_memory_dict[self.layer_idx]
+            S = v_cache.shape[2]
+            off = inference_params.sequence_len_offset
+            assert off == 0 and L <= S
+            # K cache (B, n, hd/8, S, 8), V cache (B, n, S, hd)   (mha_dejavu.py:385-447)
+            k_cache[:, :, :, :L, :] = k.permute(0, 2, 3, 1).reshape(B, n, hd // 8, 8, L).permute(0, 1, 2, 4, 3)
+            v_cache[:, :, :L, :] = v.permute(0, 2, 1, 3)
+            self.reset_decode_state(L, x.device, S)
+        ctx = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                             is_causal=True, scale=self.softmax_scale)
+        return ctx.transpose(1, 2).reshape(B, L, n * hd)
+
+    # ---- decode step ---------------------------------------------------------------------------
+    def _decode_attention(self, x, head_idx, inference_params):
+        n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
+        assert x.size(0) == 1, "the sparse decode path keeps one sequence (mha_dejavu.py:1318, 1469)"
+        k_cache, v_cache = inference_params.key_value_memory_dict[self.layer_idx]
+        S = v_cache.shape[2]
+        b = self._decode_buffers(x.device, S)
+        st = ops._stream()
+        xf = x.reshape(d).contiguous()
+        nnz = 0
+        if head_idx is not None:
+            assert head_idx.dtype == torch.int32
+            head_idx = head_idx.contiguous()
+            nnz = head_idx.numel()
+        bias = self.Wqkv.bias
+        call("djv_attn_step", b["ctx"].data_ptr(), b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
+             None if bias is None else bias.data_ptr(), xf.data_ptr(), b["x_ring"].data_ptr(), k_cache.data_ptr(),
+             v_cache.data_ptr(), b["state"].data_ptr(), None if head_idx is None else head_idx.data_ptr(), nnz, d, n,
+             hd, S, float(self.softmax_scale), b["scratch"].data_ptr(), b["scratch"].numel(), st)
+        out = torch.empty(1, d, dtype=x.dtype, device=x.device)
+        ob = self.out_proj.bias
+        state = b["state"]
+        eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
+        n_eff_ptr = state.data_ptr() + 4 * 2
+        call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
+             eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
+        call("djv_attn_step_finish", state.data_ptr(), n, st)
+        return out.view(1, 1, d)
+
+    def forward(self, x, residual, head_idx=None, mlp_sp_logit=None, seqlen=None, inference_params=None, **kwargs):
+        do_token_generation = x.size(1) == 1
+        decoding = inference_params is not None and inference_params.sequence_len_offset > 0
+        if decoding:
+            assert do_token_generation
+            out = self._decode_attention(x, head_idx if self.sparse_attention else None, inference_params)
+        else:
+            out = self.out_proj(self._prompt_attention(x, inference_params))
+        mlp_idx = None
+        if mlp_sp_logit is not None:
+            mlp_idx = ops.topk_indices(mlp_sp_logit, self.mlp_k, torch.int32)
+        if not self.skip_all_reduce:
+            out = all_reduce(out, self.process_group)
+        att_idx = None
+        if do_token_generation and self.sp is not None:
+            att_idx = ops.topk_indices(self.sp(residual), self.att_k, torch.int32)
+        return out, mlp_idx, att_idx
+
+
+class ParallelMHADejavu(ParallelMHASparseAttMlp):
+    """Dense attention + top-K of the MLP logits: forward(...) -> (out, mlp_idx) (mha_dejavu.py:910-1075)."""
+
+    sparse_attention = False
+
+    def __init__(self, embed_dim, num_heads, process_group, bias=True, dropout=0.0, softmax_scale=None,
+                 causal=False, layer_idx=None, rotary_emb_dim=0, rotary_emb_scale_base=0, use_flash_attn=False,
+                 checkpointing=False, sequence_parallel=True, device=None, dtype=None) -> None:
+        super().__init__(embed_dim, num_heads, process_group, None, bias=bias, dropout=dropout,
+                         softmax_scale=softmax_scale, causal=causal, layer_idx=layer_idx,
+                         rotary_emb_dim=rotary_emb_dim, use_flash_attn=use_flash_attn,
+                         sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+
+    def forward(self, x, residual=None, mlp_sp_logit=None, seqlen=None, inference_params=None, **kwargs):
+        out, mlp_idx, _ = super().forward(x, residual, None, mlp_sp_logit, seqlen, inference_params)
+        return out, mlp_idx
+
+
+class BlockMlpAttSparse(nn.Module):
+    """Pre-norm block threading the look-ahead state:
+    forward(hidden, residual, mixer_subset, mixer_kwargs, head_idx, mlp_sp_logit)
+        -> (hidden, residual, next_mlp_sp_logit, next_att_idx)              (block_dejavu.py:464-663)."""
+
+    returns_att_idx = True
+
+    def __init__(self, dim, mixer_cls=None, mlp_cls=None, norm_cls=nn.LayerNorm, dropout_cls=nn.Dropout,
+                 prenorm=True, resid_dropout1=0.0, resid_dropout2=0.0, drop_path1=0.0, drop_path2=0.0,
+                 fused_dropout_add_ln=False, return_residual=False, residual_in_fp32=False,
+                 sequence_parallel=False, mark_shared_params=False):
+        super().__init__()
+        assert prenorm, "OPT decoder blocks are pre-norm"
+        assert not residual_in_fp32, "the decode path keeps the residual stream in fp16"
+        self.prenorm = prenorm
+        self.mixer = mixer_cls(dim)
+        self.norm1 = norm_cls(dim)
+        self.mlp = mlp_cls(dim)
+        self.norm2 = norm_cls(dim)
+        # per-rank budgets (block_dejavu.py:549-553)
+        if hasattr(self.mlp, "sp"):
+            self.mixer.mlp_k = self.mlp.sp.K
+        if getattr(self.mixer, "sp", None) is not None:
+            self.mixer.att_k = self.mixer.sp.K
+        self.comm = None  # TensorParallelComm for the fused all-reduce + add + LayerNorm
+
+    def enable_fused_allreduce(self, comm):
+        self.comm = comm
+        self.mixer.skip_all_reduce = comm is not None
+        self.mlp.skip_all_reduce = comm is not None
+
+    def _add_norm(self, hidden_states, residual, norm, reduce_first):
+        """residual = hidden + residual; hidden = norm(residual); `hidden` may still be a rank-partial sum."""
+        decode = hidden_states.dim() == 3 and hidden_states.size(1) == 1 and hidden_states.is_cuda
+        if decode:
+            B, _, d = hidden_states.shape
+            x2 = hidden_states.reshape(B, d)
+            r2 = None if residual is None else residual.reshape(B, d)
+            if reduce_first and self.comm is not None:
+                y, r = self.comm.allreduce_add_layernorm(x2, r2, norm.weight, norm.bias, norm.eps)
+            else:
+                y, r = ops.add_layernorm(x2, r2, norm.weight, norm.bias, norm.eps)
+            return y.view(B, 1, d), r.view(B, 1, d)
+        if reduce_first and self.comm is not None:
+            hidden_states = all_reduce(hidden_states, self.mixer.process_group)
+        residual = (hidden_states + residual) if residual is not None else hidden_states
+        return norm(residual.to(dtype=norm.weight.dtype)), residual
+
+    def forward(self, hidden_states, residual=None, mixer_subset=None, mixer_kwargs=None, head_idx=None,
+                mlp_sp_logit=None, hidden_is_partial=False):
+        hidden_states, residual = self._add_norm(hidden_states, residual, self.norm1, hidden_is_partial)
+        if mixer_kwargs is None:
+            mixer_kwargs = {}
+        if self.returns_att_idx:
+            hidden_states, mlp_idx, next_att_idx = self.mixer(hidden_states, residual=residual, head_idx=head_idx,
+                                                              mlp_sp_logit=mlp_sp_logit, **mixer_kwargs)
+        else:
+            hidden_states, mlp_idx = self.mixer(hidden_states, residual=residual, mlp_sp_logit=mlp_sp_logit,
+                                                **mixer_kwargs)
+            next_att_idx = None
+        hidden_states, residual = self._add_norm(hidden_states, residual, self.norm2, self.comm is not None)
+        hidden_states, next_mlp_sp_logit = self.mlp(hidden_states, residual, mlp_idx)
+        if self.returns_att_idx:
+            return hidden_states, residual, next_mlp_sp_logit, next_att_idx
+        return hidden_states, residual, next_mlp_sp_logit
+
+
+class BlockDejavu(BlockMlpAttSparse):
+    """Block of the MLP-sparse-only model: forward(...) -> (hidden, residual, next_mlp_sp_logit)
+    (block_dejavu.py:264-461)."""
+
+    returns_att_idx = False

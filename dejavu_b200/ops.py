@@ -131,6 +131,23 @@ def gather_transposed_gemv(
     return output
 
 
+def dense_transposed_gemv(x: torch.Tensor, weight_t: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """y = x @ weight_t + bias with weight_t (M, N) contiguous (a transposed Linear weight), same kernel
+    as gather_transposed_gemv with the identity index list."""
+    M, N = weight_t.shape
+    batch, _ = x.shape
+    assert x.shape == (batch, M) and 1 <= batch <= _lib.MAX_BATCH
+    _require_cuda(x, weight_t, bias)
+    assert weight_t.stride(1) == 1 and x.dtype == weight_t.dtype == torch.float16
+    x = x.contiguous()
+    output = torch.empty(batch, N, device=x.device, dtype=x.dtype)
+    need = _lib.load().djv_gather_transposed_gemv_scratch_bytes(batch, N, M)
+    scratch = _scratch(need, x.device)
+    call("djv_gather_transposed_gemv", output.data_ptr(), weight_t.data_ptr(), x.data_ptr(), None, _ptr(bias),
+         batch, N, M, weight_t.stride(0), 0, scratch.data_ptr(), scratch.numel(), _stream())
+    return output
+
+
 def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None):
     """x (batch, d); W1 (4d, d); W2t (4d, d) = W2 transposed, contiguous; bias1 (4d); bias2 (d)."""
     x = gather_gemv(x, W1, idx, bias1, activation="relu")

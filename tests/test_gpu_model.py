@@ -1,0 +1,117 @@
+"""Model-level parity: the sparse decoder on the GPU against the CPU restatement of the reference's wiring."""
+import pytest
+import torch
+
+from oracle.model_oracle import OracleDecoder
+
+pytestmark = pytest.mark.gpu
+
+
+def tiny_config(mlp_K, att_K, n_layer=4):
+    from dejavu_b200.gpt import apply_sparsity_knobs, opt_config
+
+    cfg = opt_config("opt-125m", n_layer=n_layer, n_embd=256, hidden_size=256, n_head=4, n_inner=1024,
+                     vocab_size=512, max_position_embeddings=128, n_positions=128, mlp_sp_dim=64, att_sp_dim=32)
+    return apply_sparsity_knobs(cfg, mlp_K, att_K, att_K)
+
+
+def build(cfg, cuda, seed=0):
+    from dejavu_b200.gpt import GPTLMHeadModel
+
+    model = GPTLMHeadModel(cfg, device=cuda, dtype=torch.float16).eval()
+    return model.init_random(seed, std=0.05)
+
+
+def record_selections(model):
+    rec = []
+
+    def hook(layer_idx):
+        def fn(_m, _inp, out):
+            mlp_idx = out[1]
+            att_idx = out[2] if len(out) > 2 else None
+            rec[-1][layer_idx] = {"mlp_idx": None if mlp_idx is None else mlp_idx.cpu(),
+                                  "att_idx": None if att_idx is None else att_idx.cpu()}
+        return fn
+
+    handles = [l.mixer.register_forward_hook(hook(i)) for i, l in enumerate(model.transformer.layers)]
+    return rec, handles
+
+
+@pytest.mark.parametrize("mlp_K,att_K", [(256, 2), (256, 4), (1024, 2), (1024, 4)])
+def test_decode_matches_oracle(cuda, mlp_K, att_K):
+    """Sparse MLP + sparse attention, sparse MLP only, sparse attention only, dense."""
+    cfg = tiny_config(mlp_K, att_K)
+    model = build(cfg, cuda)
+    oracle = OracleDecoder(model.state_dict(), cfg)
+    gen = torch.Generator().manual_seed(0)
+    P, steps = 9, 36  # crosses two 16-step lazy-K/V windows
+    ids = torch.randint(0, cfg.vocab_size, (1, P), generator=gen)
+    rec, handles = record_selections(model)
+    rec.append({})
+    out = model.generate(ids.to(cuda), max_length=P + steps, cg=False, return_dict_in_generate=True,
+                         output_scores=True)
+    # replay the GPU's token sequence through the oracle, forcing (and validating) the GPU's index sets
+    ref_logits = oracle.prompt(ids[0])
+    seq = out.sequences[0].cpu()
+    assert torch.allclose(out.scores[0][0].float().cpu(), ref_logits.float(), atol=3e-2, rtol=3e-2)
+    for h in handles:
+        h.remove()
+    # the hooks fired once for the prompt pass (no selections) and once per decode step
+    model2 = build(cfg, cuda)
+    rec2, handles2 = record_selections(model2)
+    from dejavu_b200.generation import InferenceParams, allocate_kv_cache
+
+    ip = InferenceParams(max_sequence_len=P + steps, max_batch_size=1,
+                         key_value_memory_dict=allocate_kv_cache(model2, 1, P + steps, cuda))
+    rec2.append({})
+    model2(ids.to(cuda), inference_params=ip)
+    ip.sequence_len_offset = P
+    for t in range(steps - 1):
+        tok = seq[P + t].view(1, 1).to(cuda)
+        rec2.append({})
+        logits = model2(tok, position_ids=torch.tensor([[P + t]], device=cuda), inference_params=ip).logits[0, -1]
+        ip.sequence_len_offset += 1
+        forced = [rec2[-1].get(i, {}) for i in range(cfg.n_layer)]
+        ref, chosen = oracle.decode(int(seq[P + t]), P + t, forced=forced)
+        assert torch.allclose(logits.float().cpu(), ref.float(), atol=3e-2, rtol=3e-2), \
+            f"step {t}: max diff {(logits.float().cpu() - ref.float()).abs().max().item()}"
+        assert torch.allclose(logits.float().cpu(), out.scores[t + 1][0].float().cpu(), atol=1e-3), \
+            "teacher-forced replay and generate() disagree"
+    for m in model2.transformer.layers:
+        assert m.mixer.decode_status() == 0
+    for h in handles2:
+        h.remove()
+
+
+def test_cuda_graph_decode_equals_eager(cuda):
+    cfg = tiny_config(256, 2)
+    model = build(cfg, cuda)
+    gen = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (1, 7), generator=gen).to(cuda)
+    eager = model.generate(ids, max_length=7 + 40, cg=False, return_dict_in_generate=True, output_scores=True)
+    graph = model.generate(ids, max_length=7 + 40, cg=True, return_dict_in_generate=True, output_scores=True)
+    again = model.generate(ids, max_length=7 + 40, cg=True, return_dict_in_generate=True, output_scores=True)
+    assert torch.equal(eager.sequences, graph.sequences)
+    assert torch.equal(graph.sequences, again.sequences)
+    for a, b in zip(eager.scores, graph.scores):
+        assert torch.equal(a, b), "graph replay must reproduce the eager step bit for bit"
+
+
+def test_state_dict_keys_follow_the_reference(cuda):
+    cfg = tiny_config(256, 2, n_layer=2)
+    model = build(cfg, cuda)
+    keys = set(model.state_dict().keys())
+    for k in ("transformer.embeddings.word_embeddings.weight", "transformer.embeddings.position_embeddings.weight",
+              "transformer.layers.0.mixer.Wqkv.weight", "transformer.layers.0.mixer.Wqkv.bias",
+              "transformer.layers.0.mixer.out_proj.weight", "transformer.layers.0.mixer.out_proj.bias",
+              "transformer.layers.1.mixer.sp.fc0.weight", "transformer.layers.1.mixer.sp.fc1.weight",
+              "transformer.layers.0.mlp.fc1.weight", "transformer.layers.0.mlp.fc1.bias",
+              "transformer.layers.0.mlp.fc2.weight", "transformer.layers.0.mlp.fc2.bias",
+              "transformer.layers.1.mlp.sp.fc0.weight", "transformer.layers.1.mlp.sp.fc1.weight",
+              "transformer.layers.0.norm1.weight", "transformer.layers.1.norm2.bias", "transformer.ln_f.weight",
+              "lm_head.weight"):
+        assert k in keys, k
+    sd = model.state_dict()
+    assert sd["transformer.layers.0.mlp.fc2.weight"].shape == (256, 1024)
+    assert sd["transformer.layers.0.mixer.Wqkv.weight"].shape == (768, 256)
+    assert model.transformer.layers[0].mixer.mlp_k == 256 and model.transformer.layers[0].mixer.att_k == 2

@@ -187,8 +187,9 @@ def test_full_size_properties_175b_shard(cuda):
         dense = torch.relu((x.float() @ W1.float().T + b1.float()) * mask)
         close(h, dense[:, idx])
         close(y, dense.half().float() @ W2t.float(), atol=3e-3)
-        # 4. batch rows are independent: row 2 alone gives the same bits as row 2 in the batch of 4
-        assert torch.equal(ops.gather_gemv(x[2:3], W1, idx, b1, "relu")[0], h[2])
+        # 4. batch rows are independent (batch 1 and batch 4 use different lane layouts, so the fp32
+        #    sums are added in a different order: tolerance, not bits)
+        close(ops.gather_gemv(x[2:3], W1, idx, b1, "relu")[0], h[2])
     # 5. linearity of fc2 in its input
     idx = torch.randperm(F_, device=cuda, generator=gen)[:1024]
     a = torch.relu(torch.randn(1, 1024, device=cuda, generator=gen)).half()
