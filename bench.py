@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Decode benchmark of the contextual-sparse OPT path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload opt-66b] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is ONE greedy decode token of a synthetic OPT-shaped decoder (random N(0,0.02) fp16 weights,
+uniform-random prompt) after a dense prompt pass. Prints one JSON line:
+  value          decode ms/token, device-timed (CUDA events) over K graph replays; token feedback stays
+                 on the device; max over ranks
+  e2e            the same metric through the public generation loop with HOST buffers: the token id is
+                 copied from pinned host memory, the step runs, the arg-max token is read back, every step
+  roofline       the gather-GEMV (fc1) kernel at this workload's shard shape, timed live with CUDA events
+  kernels        the same for the other hot kernels
+  dense          the same model and weights with every head and neuron (dense comparator)
+  cpu_baseline   the reference's torch formulation on the host cores (bounded sample, N=1 only)
+`--impl reference` times only that CPU formulation (all host threads) and prints it in the same format.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (mlp_K, active heads, prompt tokens) — BASELINE configs 2, 3, 4
+    "opt-6.7b": (2048, 12, 128),
+    "opt-66b": (4096, 24, 128),
+    "opt-175b": (4096, 32, 512),
+    "opt-125m": (384, 4, 32),
+}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def kernel_timing(fns, iters=5):
+    """Average duration (us) of the launches in `fns` (one per layer, distinct weights), replayed as a graph."""
+    import torch
+
+    s = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        for f in fns:
+            f()
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for f in fns:
+                f()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(iters):
+            g.replay()
+        e1.record(s)
+        s.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * len(fns))
+
+
+def kernel_rooflines(model, cfg, world, peak):
+    """Times each hot kernel alone on every layer's own weights (64+ distinct matrices: far beyond L2)."""
+    import torch
+
+    from dejavu_b200 import ops
+
+    layers = list(model.transformer.layers)
+    dev = model.lm_head.weight.device
+    d, hd = cfg.hidden_size, cfg.hidden_size // cfg.n_head
+    n = layers[0].mixer.num_head_per_node
+    gen = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(1, d, device=dev, generator=gen).half()
+    out = {}
+    F_loc = layers[0].mlp.fc1.weight.shape[0]
+    K = layers[0].mixer.mlp_k or F_loc
+    idxs = [torch.randperm(F_loc, device=dev, generator=gen)[:K].sort().values.int() for _ in layers]
+    h = torch.relu(torch.randn(1, K, device=dev, generator=gen)).half()
+
+    def rec(name, us, nbytes):
+        out[name] = {"us": round(us, 2), "bytes": int(nbytes), "achieved": round(nbytes / us / 1e3, 1),
+                     "frac": round(nbytes / us / 1e3 / peak, 3)}
+
+    us = kernel_timing([lambda l=l, i=i: ops.gather_gemv(x, l.mlp.fc1.weight, i, l.mlp.fc1.bias, "relu")
+                        for l, i in zip(layers, idxs)])
+    rec("gather_gemv_fc1", us, K * d * 2 + K * 2 + K * 4 + d * 2 + K * 2)
+    us = kernel_timing([lambda l=l, i=i: ops.gather_transposed_gemv(h, l.mlp.fc2.weight_t, i, l.mlp.fc2.bias)
+                        for l, i in zip(layers, idxs)])
+    rec("gather_gemv_fc2", us, K * d * 2 + K * 2 + d * 2 + d * 2)
+    if getattr(layers[0].mlp, "sp", None) is not None:
+        R = layers[0].mlp.sp.fc0.weight.shape[0]
+        t = torch.randn(1, R, device=dev, generator=gen).half()
+        us = kernel_timing([lambda l=l: ops.dense_gemv(x, l.mlp.sp.fc0.weight) for l in layers])
+        rec("predictor_fc0", us, R * d * 2 + d * 2 + R * 2)
+        us = kernel_timing([lambda l=l: ops.dense_gemv(t, l.mlp.sp.fc1.weight) for l in layers])
+        rec("predictor_fc1", us, F_loc * R * 2 + R * 2 + F_loc * 2)
+        logits = torch.randn(F_loc, device=dev, generator=gen).half()
+        us = kernel_timing([lambda: ops.topk_indices(logits, K, torch.int32) for _ in layers])
+        out["topk"] = {"us": round(us, 2)}
+    a = layers[0].mixer.att_k or n
+    heads = [torch.randperm(n, device=dev, generator=gen)[:a].sort().values.int() for _ in layers]
+    bidx = torch.zeros(a, 1, dtype=torch.int32, device=dev)
+    us = kernel_timing([lambda l=l, hh=hh: ops.qkv_proj_sparse(
+        x, l.mixer.Wqkv.weight.view(3, n, hd, d), hh, bidx, l.mixer.Wqkv.bias.view(3, n, hd)) for l, hh in zip(layers, heads)])
+    rec("qkv_head_sparse", us, 3 * a * hd * d * 2 + 3 * a * hd * 2 + d * 2 + 3 * a * hd * 2)
+    ctx = torch.randn(1, n, hd, device=dev, generator=gen).half()
+    us = kernel_timing([lambda l=l, hh=hh: ops.out_proj_sparse(ctx, l.mixer.out_proj.weight.view(d, n, hd), hh,
+                                                               l.mixer.out_proj.bias) for l, hh in zip(layers, heads)])
+    rec("out_proj_head_sparse", us, d * a * hd * 2 + d * 2 + a * hd * 2 + d * 2)
+    return out
+
+
+def run_reference(args, cfg, mlp_K, att_K, world, rank):
+    """The reference's torch formulation on the host cores; rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import cpu_bench
+
+    r = cpu_bench.time_decode(cfg.hidden_size, cfg.n_head, cfg.n_inner, cfg.n_layer, cfg.vocab_size, mlp_K, att_K,
+                              S=256, sample_layers=1, reps=max(2, min(args.steps, 4)))
+    line = base_line(args, cfg, mlp_K, att_K, world)
+    line.update({
+        "impl": "reference", "value": round(r["ms_per_token"], 3), "ms_per_step": round(r["ms_per_token"], 3),
+        "dtype": "f32", "gpu_launches": 0,
+        "cpu_baseline": {"value": round(r["ms_per_token"], 3), "unit": "ms/token", "cores": r["cores"], "kind": "port",
+                         "sample": r["sample"]},
+        "e2e": {"value": round(r["ms_per_token"], 3), "unit": "ms/token", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    })
+    print(json.dumps(line), flush=True)
+
+
+def base_line(args, cfg, mlp_K, att_K, world):
+    return {
+        "metric": "decode_ms_per_token", "value": None, "unit": "ms/token", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}-shape decoder, batch 1, {args.promptlen} uniform-random prompt tokens, "
+                               f"greedy decode, mlp-K={mlp_K}, {att_K} active heads, TP={world}",
+                   "n_layer": cfg.n_layer, "d": cfg.hidden_size, "heads": cfg.n_head, "ffn": cfg.n_inner,
+                   "mlp_K": mlp_K, "att_K": att_K, "tp": world, "batch": 1, "promptlen": args.promptlen,
+                   "l2_policy": "weights of one decode step exceed L2 many times over; kernel timings rotate "
+                                "over every layer's own weights"},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="opt-66b", choices=sorted(WORKLOADS))
+    ap.add_argument("--mlp-K", type=int, default=None)
+    ap.add_argument("--att-K1", type=int, default=None)
+    ap.add_argument("--att-K2", type=int, default=None)
+    ap.add_argument("--promptlen", type=int, default=None)
+    ap.add_argument("--n-layer", type=int, default=None, help="debug: fewer layers (invalid as a bench number)")
+    ap.add_argument("--no-dense", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--fused-allreduce", type=int, default=1)
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    d_mlp_K, d_att_K, d_prompt = WORKLOADS[args.workload]
+    mlp_K = args.mlp_K or d_mlp_K
+    att_K1 = args.att_K1 or d_att_K
+    att_K2 = args.att_K2 or att_K1
+    args.promptlen = args.promptlen or d_prompt
+    args.warmup = max(args.warmup, 3)
+
+    from dejavu_b200.gpt import GPTLMHeadModel, apply_sparsity_knobs, opt_config
+
+    cfg = opt_config(args.workload)
+    if args.n_layer:
+        cfg.n_layer = args.n_layer
+    apply_sparsity_knobs(cfg, mlp_K, att_K1, att_K2, world)
+
+    if args.impl == "reference":
+        run_reference(args, cfg, mlp_K if cfg.mlp_sparse else None, att_K1 if cfg.att_sparse else None, world, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from dejavu_b200 import _lib
+    from dejavu_b200.generation import update_graph_cache
+
+    _lib.load()  # fail loudly if the CUDA library is missing
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    pg = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        pg = dist.group.WORLD
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_build = time.time()
+    model = GPTLMHeadModel(cfg, process_group=pg, device=dev, dtype=torch.float16).eval()
+    model.init_random(seed=0)
+    comm = None
+    if world > 1 and args.fused_allreduce:
+        from dejavu_b200.comm import TensorParallelComm
+
+        comm = TensorParallelComm(pg, dev, max_bytes=cfg.hidden_size * 2)
+        model.transformer.enable_fused_allreduce(comm)
+    torch.cuda.synchronize()
+    t_build = time.time() - t_build
+
+    K, W, P = args.steps, args.warmup, args.promptlen
+    S = P + 2 * (W + K) + 64
+    gen = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab_size, (1, P), generator=gen).to(dev)
+
+    def timed_decode(label):
+        """prompt pass, W warm-up steps, K timed steps (device feedback), then K steps through host buffers."""
+        with torch.inference_mode():
+            cache = update_graph_cache(model, None, 1, P, S, greedy_feedback=True, vocab_size=cfg.vocab_size)
+            per_step = cache.launches_per_step
+            ip = cache.inference_params
+            ip.sequence_len_offset = 0
+            logits = model(prompt, inference_params=ip).logits[:, -1, :cfg.vocab_size]
+            ip.sequence_len_offset = P
+            cache.input_ids.copy_(logits.argmax(-1, keepdim=True))
+            cache.position_ids.fill_(P)
+            for _ in range(W):
+                cache.graph.replay()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(local_rank) as clocks:
+                e0.record()
+                for _ in range(K):
+                    cache.graph.replay()
+                e1.record()
+                barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1) / K)
+            # end to end: host token in, host token out, every step
+            tok_h = torch.zeros(1, 1, dtype=torch.long).pin_memory()
+            pos_h = torch.zeros(1, 1, dtype=torch.long).pin_memory()
+            out_h = torch.zeros(1, 1, dtype=torch.long).pin_memory()
+            out_h.copy_(cache.next_token)
+            torch.cuda.synchronize()
+            position = P + W + K
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(K):
+                tok_h.copy_(out_h)
+                pos_h.fill_(position)
+                cache.input_ids.copy_(tok_h, non_blocking=True)
+                cache.position_ids.copy_(pos_h, non_blocking=True)
+                cache.graph.replay()
+                out_h.copy_(cache.next_token, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                position += 1
+            barrier()
+            e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / K)
+            status = [l.mixer.decode_status() for l in model.transformer.layers]
+            assert all(s == 0 for s in status), f"{label}: a decode kernel reported a bad state {status}"
+            if comm is not None:
+                assert comm.status() == 0, "fused all-reduce reported a timeout"
+            del cache
+        return ms, e2e_ms, per_step, clocks.summary()
+
+    ms, e2e_ms, per_step, clocks = timed_decode("sparse")
+    line = base_line(args, cfg, mlp_K, att_K1, world)
+    peak, peak_kind = measured_peaks()
+    line.update({
+        "value": round(ms, 4), "ms_per_step": round(ms, 4), "clocks": clocks,
+        "e2e": {"value": round(e2e_ms, 4), "unit": "ms/token", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 8},
+        "gpu_launches": int(per_step * K), "launches_per_step": int(per_step),
+        "build_s": round(t_build, 1),
+    })
+    if args.n_layer:
+        line["config"]["debug_n_layer"] = args.n_layer
+
+    if not args.no_dense:
+        model.transformer.set_dense(True)
+        dms, de2e, dper, _ = timed_decode("dense")
+        model.transformer.set_dense(False)
+        line["dense"] = {"ms_per_token": round(dms, 4), "e2e_ms_per_token": round(de2e, 4),
+                         "launches_per_step": int(dper), "speedup_sparse_vs_dense": round(dms / ms, 3)}
+
+    with torch.inference_mode():
+        kern = kernel_rooflines(model, cfg, world, peak)
+    top = kern["gather_gemv_fc1"]
+    line["roofline"] = {"kernel": "rowdot_kernel (gather GEMV fc1)", "bound": "hbm", "achieved": top["achieved"],
+                        "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": top["frac"],
+                        "traffic": None, "algorithmic_bytes": top["bytes"], "us_per_launch": top["us"]}
+    line["kernels"] = kern
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        from oracle import cpu_bench
+
+        r = cpu_bench.time_decode(cfg.hidden_size, cfg.n_head, cfg.n_inner, cfg.n_layer, cfg.vocab_size,
+                                  mlp_K if cfg.mlp_sparse else None, att_K1 if cfg.att_sparse else None)
+        line["cpu_baseline"] = {"value": round(r["ms_per_token"], 2), "unit": "ms/token", "cores": r["cores"],
+                                "kind": "port", "sample": r["sample"]}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        if comm is not None:
+            comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -58,7 +58,8 @@ class DecodingCGCache:
     input_ids: Optional[torch.Tensor] = None
     position_ids: Optional[torch.Tensor] = None
     logits: Optional[torch.Tensor] = None
-    mempool: object = None
+    next_token: Optional[torch.Tensor] = None
+    launches_per_step: int = 0
 
     def run(self, new_input_ids, new_position_ids):
         self.input_ids.copy_(new_input_ids)
@@ -69,10 +70,12 @@ class DecodingCGCache:
 
 @torch.inference_mode()
 def update_graph_cache(model, cache, batch_size, seqlen_og, max_seqlen, tensor_parallel=1, dtype=None,
-                       n_warmups=2):
+                       n_warmups=2, greedy_feedback=False, vocab_size=None):
     """(Re)allocates the K/V caches for (batch_size, max_seqlen) and captures ONE decode step of `model`
     into a CUDA graph. Capture launches nothing; the warm-up steps before it do run, and leave the lazy-K/V
-    state wherever they leave it — the prompt pass of every generate() call resets that state."""
+    state wherever they leave it — the prompt pass of every generate() call resets that state.
+    With greedy_feedback the graph also takes the arg-max of the logits, writes it back into input_ids and
+    advances position_ids, so a replay is one complete greedy decode step with no host work."""
     if cache is None:
         cache = DecodingCGCache()
     param = next(iter(model.parameters()))
@@ -95,18 +98,28 @@ def update_graph_cache(model, cache, batch_size, seqlen_og, max_seqlen, tensor_p
         layer.mixer.reset_decode_state(seqlen_og, device, max_seqlen)
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
+    def step():
+        cache.logits = model(cache.input_ids, position_ids=cache.position_ids,
+                             inference_params=cache.inference_params).logits
+        if greedy_feedback:
+            cache.next_token = cache.logits[:, -1, :vocab_size].argmax(dim=-1, keepdim=True)
+            cache.input_ids.copy_(cache.next_token)
+            cache.position_ids.add_(1)
+
     with torch.cuda.stream(s):
         for _ in range(n_warmups):
-            cache.logits = model(cache.input_ids, position_ids=cache.position_ids,
-                                 inference_params=cache.inference_params).logits
+            step()
         s.synchronize()
         if torch.distributed.is_initialized():
             torch.distributed.barrier()
     torch.cuda.current_stream().wait_stream(s)
     graph = torch.cuda.CUDAGraph()
+    from . import _lib
+
+    launches_before = _lib.launch_count()
     with torch.cuda.graph(graph):
-        cache.logits = model(cache.input_ids, position_ids=cache.position_ids,
-                             inference_params=cache.inference_params).logits
+        step()
+    cache.launches_per_step = _lib.launch_count() - launches_before  # kernels of libdejavu_b200 per replay
     cache.graph = graph
     return cache
 

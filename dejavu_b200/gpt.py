@@ -171,6 +171,16 @@ class GPTModel(nn.Module):
         for layer in self.layers:
             layer.enable_fused_allreduce(comm)
 
+    def set_dense(self, dense: bool, cublas: bool = True):
+        """Dense comparator mode on the SAME weights: every head and every neuron, no predictors (what
+        --mlp-K ffn --att-K heads gives, Dejavu/benchmarks/benchmark_generation_opt.py); with `cublas` the
+        dense MLP GEMVs of the decode step go through torch."""
+        self.force_dense = dense
+        for layer in self.layers:
+            layer.mixer.run_predictor = not dense
+            layer.mlp.run_predictor = not dense
+            layer.mlp.dense_decode_cublas = dense and cublas
+
     def forward(self, input_ids, position_ids=None, inference_params=None):
         hidden_states = self.embeddings(input_ids, position_ids=position_ids)
         residual = None

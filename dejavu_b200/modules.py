@@ -149,6 +149,8 @@ class ParallelFusedMLPDejavu(nn.Module):
     (fused_dense_sparse_dejavu.py:821-951)."""
 
     has_predictor = True
+    run_predictor = True         # False: dense comparator mode, skip the look-ahead predictor
+    dense_decode_cublas = False  # True: dense decode GEMVs through torch (cuBLAS)
 
     def __init__(self, in_features, hidden_features, sp_kwargs, out_features=None, activation="gelu_approx",
                  layer_idx=None, process_group=None, bias1=True, bias2=True, sequence_parallel=True,
@@ -184,7 +186,7 @@ class ParallelFusedMLPDejavu(nn.Module):
             out = ops.mlp_sparse(x.view(x.size(0), -1), self.fc1.weight, self.fc2.weight_t, idx, self.fc1.bias,
                                  self.fc2.bias)
             out = out.view(x.size(0), 1, -1)
-        elif do_token_generation:
+        elif do_token_generation and not self.dense_decode_cublas:
             act = "relu" if self.activation == "relu" else "gelu_approx"
             h = ops.dense_gemv(x.view(x.size(0), -1), self.fc1.weight, self.fc1.bias, act)
             out = ops.dense_transposed_gemv(h, self.fc2.weight_t, self.fc2.bias).view(x.size(0), 1, -1)
@@ -194,7 +196,7 @@ class ParallelFusedMLPDejavu(nn.Module):
             out = F.linear(h, self.fc2.weight, self.fc2.bias)
         if not self.skip_all_reduce:
             out = all_reduce(out, self.process_group)
-        mlp_logit = self.sp(residual) if (do_token_generation and self.has_predictor) else None
+        mlp_logit = self.sp(residual) if (do_token_generation and self.has_predictor and self.run_predictor) else None
         return out, mlp_logit
 
 
@@ -226,6 +228,7 @@ class ParallelMHASparseAttMlp(nn.Module):
     att_idx = top-att_k of sp(residual) for the NEXT layer's attention (mha_dejavu.py:1152-1511)."""
 
     sparse_attention = True
+    run_predictor = True  # False: dense comparator mode, skip the look-ahead predictor
 
     def __init__(self, embed_dim, num_heads, process_group, sp_kwargs, bias=True, dropout=0.0,
                  softmax_scale=None, causal=False, layer_idx=None, rotary_emb_dim=0, rotary_emb_scale_base=0,
@@ -344,7 +347,7 @@ class ParallelMHASparseAttMlp(nn.Module):
         if not self.skip_all_reduce:
             out = all_reduce(out, self.process_group)
         att_idx = None
-        if do_token_generation and self.sp is not None:
+        if do_token_generation and self.sp is not None and self.run_predictor:
             att_idx = ops.topk_indices(self.sp(residual), self.att_k, torch.int32)
         return out, mlp_idx, att_idx
 
