@@ -37,6 +37,7 @@ SIGNATURES = {
     "djv_gather_gemv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _i, _vp]),
     "djv_gather_transposed_gemv_scratch_bytes": (_sz, [_i, _i, _i]),
     "djv_gather_transposed_gemv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _sz, _vp]),
+    "djv_gather_transposed_gemv_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp]),
     "djv_mlp_sparse": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
     "djv_topk": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "djv_qkv_proj_sparse": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),

@@ -75,6 +75,24 @@ int djv_gather_transposed_gemv(void *y, const void *w, const void *x, const void
                                void *scratch, size_t scratch_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The same product as djv_gather_transposed_gemv, for callers that have no scratch memory to give.
+ * This entry point has no counterpart in the reference: it exists for hosts that cannot allocate device
+ * memory at the call site (all of it already handed to their own pool, allocation forbidden in the calling
+ * context, or a binding with no workspace concept).
+ * The scratch is a built-in device array of DJV_STATIC_SCRATCH_BYTES that every GPU loading the library
+ * holds until exit; requests that need more (large B*N with many row chunks) are refused with
+ * DJV_ERR_SCRATCH and a message. The call allocates and frees nothing. The first call made while a given
+ * device is current resolves the array's device address: issue that first call outside of any stream
+ * capture. All calls on a device share the array, so calls that could overlap on the GPU must be ordered
+ * by the caller; the array's previous contents never influence a result.
+ *   1 <= B <= 4, M >= 1; other arguments as djv_gather_transposed_gemv.
+ * ------------------------------------------------------------------------------------------- */
+#define DJV_STATIC_SCRATCH_BYTES (4096u + (256u << 10))
+int djv_gather_transposed_gemv_static(void *y, const void *w, const void *x, const void *idx,
+                                      const void *bias, int B, int N, int M, long long ldw, int idx_is_64,
+                                      void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Sparse MLP in one call: y = gather_transposed_gemv(relu(gather_gemv(x,W1,idx,b1)), W2t, idx, b2).
  * Replaces mlp_sparse, Dejavu/src/ops/triton/gather_gemv.py:647-657. h is rounded to fp16 between
  * the two products exactly as there (:233). h (B,M) fp16 is caller-provided workspace.
