@@ -27,7 +27,13 @@ struct djv_comm {
 namespace djv {
 
 constexpr int AR_MAX_WORLD = 8;
-constexpr unsigned AR_SPIN_LIMIT = 1u << 22;  // x ~100 ns back-off: gives up after roughly a second
+constexpr unsigned long long AR_WAIT_LIMIT_NS = 2000ull * 1000 * 1000;  // a wait on a peer gives up after 2 s
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -62,6 +68,8 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *const *
   const int nchunks = d / 8;
   const int total_chunks = B * nchunks;
   if (tid == 0) failed = 0;
+  // once a wait has run out the exchange is dead: later calls return at once instead of waiting again
+  if (epoch_status[1] != 0u) return;
 
   // 1. publish this rank's partial
   {
@@ -75,10 +83,10 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *const *
     __threadfence_system();
     st_release_sys(flags[tid] + rank, want);
     const unsigned *f = flags[rank] + tid;
-    unsigned spins = 0;
+    const unsigned long long t_start = global_timer_ns();
     // flags only grow; a later epoch from a faster peer also satisfies the wait
     while ((int)(ld_acquire_sys(f) - want) < 0) {
-      if (++spins > AR_SPIN_LIMIT) {
+      if (global_timer_ns() - t_start > AR_WAIT_LIMIT_NS) {
         failed = 1;
         break;
       }
