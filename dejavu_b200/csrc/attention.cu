@@ -15,7 +15,7 @@ namespace djv {
 // ------------------------------------------------------------------------------------------
 // state words, see DJV_ATTN_STATE_* in the header
 // ------------------------------------------------------------------------------------------
-enum { ST_SLOT = 0, ST_BASE = 1, ST_NEFF = 2, ST_STATUS = 3 };
+enum { ST_SLOT = 0, ST_BASE = 1, ST_NEFF = 2, ST_STATUS = 3, ST_OPEN = 4 };  // ST_OPEN: a step awaits its advance
 __device__ __forceinline__ int *st_pending(int *st) { return st + DJV_ATTN_STATE_HDR; }
 __device__ __forceinline__ int *st_eff(int *st, int nheads) { return st + DJV_ATTN_STATE_HDR + nheads; }
 __device__ __forceinline__ int *st_rowmask(int *st, int nheads) {
@@ -34,7 +34,20 @@ __global__ void __launch_bounds__(1024)
 attn_prep_kernel(int *__restrict__ st, const int *__restrict__ head_idx, int nnz,
                  const __half *__restrict__ x, __half *__restrict__ x_ring, int d, int nheads, int S) {
   const int tid = threadIdx.x;
-  const int slot = st[ST_SLOT], base = st[ST_BASE];
+  int slot = st[ST_SLOT], base = st[ST_BASE];
+  // the previous step was not closed by djv_attn_step_finish: advance past it first
+  if (st[ST_OPEN] != 0 && st[ST_STATUS] == 0) {
+    if (++slot >= DJV_KV_WINDOW) {
+      slot = 0;
+      base += DJV_KV_WINDOW;
+    }
+  }
+  __syncthreads();  // every thread has read the old words
+  if (tid == 0) {
+    st[ST_SLOT] = slot;
+    st[ST_BASE] = base;
+    st[ST_OPEN] = 1;
+  }
   int *pending = st_pending(st), *eff = st_eff(st, nheads), *rowmask = st_rowmask(st, nheads);
   const bool bad = slot < 0 || slot >= DJV_KV_WINDOW || base < 0 || base + slot >= S;
   if (bad) {
@@ -88,7 +101,8 @@ attn_prep_kernel(int *__restrict__ st, const int *__restrict__ head_idx, int nnz
 }
 
 __global__ void attn_finish_kernel(int *st) {
-  if (threadIdx.x == 0 && st[ST_STATUS] == 0) {
+  if (threadIdx.x == 0 && st[ST_STATUS] == 0 && st[ST_OPEN] != 0) {
+    st[ST_OPEN] = 0;
     int slot = st[ST_SLOT] + 1;
     if (slot >= DJV_KV_WINDOW) {
       slot = 0;

@@ -23,7 +23,7 @@ from . import ops
 from .generation import GenerationMixin
 from .modules import (BlockDejavu, BlockMlpAttSparse, ColumnParallelLinear, ParallelFusedMLP,
                       ParallelFusedMLPDejavu, ParallelMHADejavu, ParallelMHASparseAttMlp, _rank, _world,
-                      all_reduce)
+                      all_reduce, join_side_streams)
 
 # (n_layer, d, heads, ffn) of the OPT family; vocab 50272, 2048 positions (+2 offset rows dropped at load,
 # Dejavu/src/utils/dejavu_util.py:41-46), ReLU, pre-norm, tied embeddings, all biases present.
@@ -200,6 +200,8 @@ class GPTModel(nn.Module):
         # final residual add + ln_f (gpt_dejavu.py:606-610)
         last = self.layers[-1]
         hidden_states, _ = last._add_norm(hidden_states, residual, self.ln_f, partial_in)
+        if hidden_states.is_cuda:
+            join_side_streams(hidden_states.device)  # the last layer's look-ahead results have no consumer
         return hidden_states
 
 

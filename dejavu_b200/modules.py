@@ -15,13 +15,14 @@ Differences that are deliberate (none changes results for heads / neurons that a
     the others);
   * fc2's weight is stored once, transposed (ffn_local, d); `fc2.weight` is a (d, ffn_local) view of it,
     so nothing is duplicated or built lazily inside forward;
-  * the predictor look-ahead work runs on the same stream as the rest of the step (the whole step is
-    one CUDA graph); the reference's side stream is an overlap device, not a semantic one.
+  * the predictor look-ahead work runs on side streams like the reference's sp_stream, but consumers
+    wait on per-result events where the result is used, not at the end of the producing module.
 The prompt phase (seqlen > 1) is dense and uses torch (cuBLAS / SDPA), as in the reference.
 """
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -32,6 +33,76 @@ from . import _lib, ops
 from ._lib import call
 
 KV_WINDOW = _lib.KV_WINDOW
+
+# Look-ahead predictor work runs on two side streams per device ("att": head predictor, "mlp": MLP
+# predictor + its top-K), forked from and joined to the main stream with events; inside a CUDA-graph
+# capture these become parallel branches of the graph. DJV_SIDE_STREAMS=0 keeps everything on one stream.
+SIDE_STREAMS_ENABLED = os.environ.get("DJV_SIDE_STREAMS", "1") != "0"
+_SIDE_STREAMS: dict = {}
+_SIDE_DIRTY: dict = {}  # device index -> names of side streams forked since the last join
+
+
+def side_streams(device) -> dict:
+    key = torch.device(device).index
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = {"att": torch.cuda.Stream(device=device), "mlp": torch.cuda.Stream(device=device)}
+    return _SIDE_STREAMS[key]
+
+
+class _side:
+    """`with _side(ref, name, after=t) as done: r = work(); done(r)` runs work() on side stream `name` after
+    everything queued on the current stream so far and after `t` is ready; done(r) attaches the completion
+    event to r, which consumers honour with _wait_ready(r)."""
+
+    def __init__(self, ref, name, after=None):
+        self.active = SIDE_STREAMS_ENABLED and ref.is_cuda
+        self.ref, self.name, self.after, self.ctx = ref, name, after, None
+
+    def __enter__(self):
+        if not self.active:
+            return lambda t: None
+        self.main = torch.cuda.current_stream()
+        self.side = side_streams(self.ref.device)[self.name]
+        fork = torch.cuda.Event()
+        fork.record(self.main)
+        self.side.wait_event(fork)
+        _SIDE_DIRTY.setdefault(self.ref.device.index, set()).add(self.name)
+        if self.after is not None:
+            ev = getattr(self.after, "_ready_event", None)
+            if ev is not None:
+                self.side.wait_event(ev)
+            self.after.record_stream(self.side)
+        self.ctx = torch.cuda.stream(self.side)
+        self.ctx.__enter__()
+        return self._done
+
+    def _done(self, t):
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        t._ready_event = ev
+        t.record_stream(self.main)
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+        return False
+
+
+def _wait_ready(t):
+    """Make the current stream wait for a tensor produced on a side stream (no-op otherwise)."""
+    ev = None if t is None else getattr(t, "_ready_event", None)
+    if ev is not None:
+        torch.cuda.current_stream().wait_event(ev)
+
+
+def join_side_streams(device):
+    """All side-stream work rejoins the current stream (needed before a graph capture ends)."""
+    key = torch.device(device).index
+    dirty = _SIDE_DIRTY.pop(key, None)
+    if dirty:
+        main = torch.cuda.current_stream()
+        for name in dirty:
+            main.wait_stream(_SIDE_STREAMS[key][name])
 
 
 def _world(pg) -> int:
@@ -180,6 +251,12 @@ class ParallelFusedMLPDejavu(nn.Module):
 
     def forward(self, x, residual, idx=None):
         do_token_generation = x.size(1) == 1
+        # the look-ahead predictor for the NEXT layer runs beside this MLP (fused_dense_sparse_dejavu.py:942-949)
+        mlp_logit = None
+        if do_token_generation and self.has_predictor and self.run_predictor:
+            with _side(x, "mlp", after=residual) as done:
+                mlp_logit = self.sp(residual)
+                done(mlp_logit)
         if idx is not None:
             assert x.size(1) == 1
             assert self.activation == "relu", "the sparse path applies ReLU (gather_gemv.py:655)"
@@ -196,7 +273,6 @@ class ParallelFusedMLPDejavu(nn.Module):
             out = F.linear(h, self.fc2.weight, self.fc2.bias)
         if not self.skip_all_reduce:
             out = all_reduce(out, self.process_group)
-        mlp_logit = self.sp(residual) if (do_token_generation and self.has_predictor and self.run_predictor) else None
         return out, mlp_logit
 
 
@@ -330,25 +406,34 @@ class ParallelMHASparseAttMlp(nn.Module):
         n_eff_ptr = state.data_ptr() + 4 * 2
         call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
              eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
-        call("djv_attn_step_finish", state.data_ptr(), n, st)
+        # the window advance is folded into the next step's first kernel (no djv_attn_step_finish launch)
         return out.view(1, 1, d)
 
     def forward(self, x, residual, head_idx=None, mlp_sp_logit=None, seqlen=None, inference_params=None, **kwargs):
         do_token_generation = x.size(1) == 1
         decoding = inference_params is not None and inference_params.sequence_len_offset > 0
+        # Look-ahead work runs beside the attention, as in the reference (sp_stream, mha_dejavu.py:1364-1370,
+        # 1501-1510): the MLP top-K continues on the stream that produced the logits, the head predictor
+        # forks from here; consumers wait on the event attached to each result.
+        mlp_idx = None
+        if mlp_sp_logit is not None:
+            with _side(x, "mlp", after=mlp_sp_logit) as done:
+                mlp_idx = ops.topk_indices(mlp_sp_logit, self.mlp_k, torch.int32)
+                done(mlp_idx)
+        att_idx = None
+        if do_token_generation and self.sp is not None and self.run_predictor:
+            with _side(x, "att", after=residual) as done:
+                att_idx = ops.topk_indices(self.sp(residual), self.att_k, torch.int32)
+                done(att_idx)
         if decoding:
             assert do_token_generation
+            _wait_ready(head_idx)
             out = self._decode_attention(x, head_idx if self.sparse_attention else None, inference_params)
         else:
             out = self.out_proj(self._prompt_attention(x, inference_params))
-        mlp_idx = None
-        if mlp_sp_logit is not None:
-            mlp_idx = ops.topk_indices(mlp_sp_logit, self.mlp_k, torch.int32)
         if not self.skip_all_reduce:
             out = all_reduce(out, self.process_group)
-        att_idx = None
-        if do_token_generation and self.sp is not None and self.run_predictor:
-            att_idx = ops.topk_indices(self.sp(residual), self.att_k, torch.int32)
+        _wait_ready(mlp_idx)  # this layer's MLP is next on the main stream
         return out, mlp_idx, att_idx
 
 
