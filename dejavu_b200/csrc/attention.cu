@@ -389,19 +389,34 @@ __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) oacc[e] *= corr;
     m_run = m_new;
-    // P.V: CH lanes cover one V row, RPI rows per iteration
-    for (int t = vrow; t < pn; t += RPI) {
-      const uint4 vv = ld_stream16(Vh + (size_t)(p0 + t) * HD + vch * 8);
-      const float p = sc[t];
-      const float2 v0 = h2f(vv.x), v1 = h2f(vv.y), v2 = h2f(vv.z), v3 = h2f(vv.w);
-      oacc[0] = fmaf(p, v0.x, oacc[0]);
-      oacc[1] = fmaf(p, v0.y, oacc[1]);
-      oacc[2] = fmaf(p, v1.x, oacc[2]);
-      oacc[3] = fmaf(p, v1.y, oacc[3]);
-      oacc[4] = fmaf(p, v2.x, oacc[4]);
-      oacc[5] = fmaf(p, v2.y, oacc[5]);
-      oacc[6] = fmaf(p, v3.x, oacc[6]);
-      oacc[7] = fmaf(p, v3.y, oacc[7]);
+    // P.V: CH lanes cover one V row, RPI rows per iteration, 4 iterations' loads in flight
+    for (int t0 = vrow; t0 < pn; t0 += RPI * 4) {
+      uint4 vv[4];
+      float pw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int t = t0 + u * RPI;
+        if (t < pn) {
+          vv[u] = ld_stream16(Vh + (size_t)(p0 + t) * HD + vch * 8);
+          pw[u] = sc[t];
+        } else {
+          vv[u] = make_uint4(0, 0, 0, 0);
+          pw[u] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float p = pw[u];
+        const float2 v0 = h2f(vv[u].x), v1 = h2f(vv[u].y), v2 = h2f(vv[u].z), v3 = h2f(vv[u].w);
+        oacc[0] = fmaf(p, v0.x, oacc[0]);
+        oacc[1] = fmaf(p, v0.y, oacc[1]);
+        oacc[2] = fmaf(p, v1.x, oacc[2]);
+        oacc[3] = fmaf(p, v1.y, oacc[3]);
+        oacc[4] = fmaf(p, v2.x, oacc[4]);
+        oacc[5] = fmaf(p, v2.y, oacc[5]);
+        oacc[6] = fmaf(p, v3.x, oacc[6]);
+        oacc[7] = fmaf(p, v3.y, oacc[7]);
+      }
     }
     __syncthreads();  // sc[] and redf[] are reused by the next pass
   }
