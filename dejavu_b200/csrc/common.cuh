@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "../../include/dejavu_b200.h"
 
@@ -25,6 +26,11 @@ int check_launch(const char *what);  // cudaGetLastError -> status
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int sm_count();  // multiprocessors of the current device (cached per device)
+// integer development knob from the environment (callers read it once into a static)
+inline int env_int(const char *name, int dflt) {
+  const char *v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
 
 // ---- device side --------------------------------------------------------------------------
 constexpr int WARP = 32;

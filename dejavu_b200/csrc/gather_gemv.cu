@@ -11,6 +11,7 @@
 //   rowaxpy : M*N*2 + B*M*2 (x) + N*2 (bias) + B*N*2 (y)
 #include "common.cuh"
 #include "rowaxpy.cuh"
+#include "rowdot_mma.cuh"
 
 namespace djv {
 
@@ -234,6 +235,19 @@ extern "C" int djv_gather_gemv(void *y, const void *w, const void *x, const void
   DJV_REQUIRE(act >= DJV_ACT_ID && act <= DJV_ACT_SQUARED_RELU, "gather_gemv: unknown activation %d", act);
   if (M == 0) return DJV_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Enough activation rows make this a real small-N contraction: tensor cores. Measured cross-over on B200
+  // (d = 12288): above 8 rows always; for 3..8 rows only when there are >= 256 tiles of 16 gathered rows
+  // (the CUDA-core kernel, one slice of <= 8 rows at a time, wins on short index lists).
+  static const int k_mma_min_b = env_int("DJV_MMA_MIN_B", 3);
+  static const int k_mma_min_tiles = env_int("DJV_MMA_MIN_TILES", 256);
+  if (B > 8 || (B >= k_mma_min_b && ceil_div(M, MM_ROWS) >= k_mma_min_tiles)) {
+    rc = rowdot_mma(B, act, static_cast<__half *>(y), static_cast<const __half *>(w),
+                    static_cast<const __half *>(x), idx, static_cast<const __half *>(bias), M, N, ldw,
+                    idx_is_64, st);
+    if (rc) return rc;
+    count_launch();
+    return check_launch("gather_gemv");
+  }
   for (int b0 = 0; b0 < B; b0 += 8) {
     const int bs = (B - b0 < 8) ? (B - b0) : 8;
     rc = rowdot_slice(bs, act, static_cast<__half *>(y) + (size_t)b0 * M, static_cast<const __half *>(w),

@@ -83,6 +83,10 @@ GATHER_CASES = [
     (512, 256, 64, 8, "rand32"),
     (512, 256, 64, 16, "rand32"),      # batch cut into slices
     (512, 256, 33, 32, "rand64"),
+    (6144, 12288, 512, 16, "rand32"),  # tensor-core path at the 175B shard shape
+    (6144, 12288, 100, 9, "rand64"),
+    (2048, 1000, 300, 24, "rand32"),   # row length not a multiple of 32
+    (4608, 9216, 77, 32, "dup32"),
 ]
 
 
