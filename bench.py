@@ -200,7 +200,7 @@ def run_reference(args, cfg, mlp_K, att_K, world, rank):
         "e2e": {"value": round(r["ms_per_token"], 3), "unit": "ms/token", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     })
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def base_line(args, cfg, mlp_K, att_K, world):
@@ -217,7 +217,30 @@ def base_line(args, cfg, mlp_K, att_K, world):
     }
 
 
+_RESULT_FD = None
+
+
+def quiet_stdout():
+    """Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line there.
+    Everything written to fd 1 from now on goes to stderr; emit() writes the result to the real stdout."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    quiet_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -387,7 +410,7 @@ def main():
         line["cpu_baseline"] = {"value": round(r["ms_per_token"], 2), "unit": "ms/token", "cores": r["cores"],
                                 "kind": "port", "sample": r["sample"]}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         if comm is not None:
             comm.close()

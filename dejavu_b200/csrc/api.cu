@@ -28,6 +28,11 @@ int check_launch(const char *what) {
   return DJV_OK;
 }
 
+bool pdl_enabled() {
+  static const bool on = env_int("DJV_PDL", 1) != 0;
+  return on;
+}
+
 int sm_count() {
   static int cached[64];
   int dev = 0;

@@ -23,6 +23,7 @@ __device__ __forceinline__ int *st_rowmask(int *st, int nheads) {
 }
 
 __global__ void attn_state_reset_kernel(int *st, int nheads, int prompt_len) {
+  pdl_prologue();
   const int words = DJV_ATTN_STATE_WORDS(nheads);
   for (int i = threadIdx.x; i < words; i += blockDim.x) st[i] = 0;
   __syncthreads();
@@ -33,6 +34,7 @@ __global__ void attn_state_reset_kernel(int *st, int nheads, int prompt_len) {
 __global__ void __launch_bounds__(1024)
 attn_prep_kernel(int *__restrict__ st, const int *__restrict__ head_idx, int nnz,
                  const __half *__restrict__ x, __half *__restrict__ x_ring, int d, int nheads, int S) {
+  pdl_prologue();
   const int tid = threadIdx.x;
   int slot = st[ST_SLOT], base = st[ST_BASE];
   // the previous step was not closed by djv_attn_step_finish: advance past it first
@@ -101,6 +103,7 @@ attn_prep_kernel(int *__restrict__ st, const int *__restrict__ head_idx, int nnz
 }
 
 __global__ void attn_finish_kernel(int *st) {
+  pdl_prologue();
   if (threadIdx.x == 0 && st[ST_STATUS] == 0 && st[ST_OPEN] != 0) {
     st[ST_OPEN] = 0;
     int slot = st[ST_SLOT] + 1;
@@ -121,7 +124,6 @@ __global__ void attn_finish_kernel(int *st) {
 // ------------------------------------------------------------------------------------------
 constexpr int QKV_THREADS = 256;
 constexpr int QKV_WARPS = QKV_THREADS / WARP;
-constexpr int QKV_RPB = 8;
 
 struct QkvArgs {
   const __half *w;     // (3,nheads,hd,d)
@@ -138,41 +140,57 @@ struct QkvArgs {
   int S;
 };
 
-template <int NB, int WPR>
-__device__ __forceinline__ void multi_rowdot(const uint4 *wp, const uint4 *(&xp)[NB], int nchunks,
-                                             int glane, float (&acc)[NB]) {
+// ROWS weight rows against NB token rows: every activation chunk is loaded (through L1) once and used for
+// all ROWS weight rows, so L1 traffic per weight byte is NB / ROWS. Without that sharing a head with three
+// pending token rows reads 3 bytes of x per byte of weight and the kernel is bound by L1 bandwidth, not HBM.
+template <int NB, int WPR, int ROWS, int U>
+__device__ __forceinline__ void multi_rowdot(const uint4 *const (&wp)[ROWS], const uint4 *const (&xp)[NB],
+                                             int nchunks, int glane, float (&acc)[ROWS][NB]) {
   constexpr int GLANES = WARP * WPR;
-  constexpr int U = 4;
 #pragma unroll
-  for (int r = 0; r < NB; ++r) acc[r] = 0.f;
+  for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+    for (int r = 0; r < NB; ++r) acc[j][r] = 0.f;
   for (int c0 = glane; c0 < nchunks; c0 += GLANES * U) {
-    uint4 wv[U];
+    uint4 wv[ROWS][U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int c = c0 + u * GLANES;
-      wv[u] = (c < nchunks) ? ld_stream16(wp + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < ROWS; ++j) wv[j][u] = (c < nchunks) ? ld_stream16(wp[j] + c) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int c = c0 + u * GLANES;
       if (c < nchunks) {
 #pragma unroll
-        for (int r = 0; r < NB; ++r) acc[r] = dot8(wv[u], ld_cached16(xp[r] + c), acc[r]);
+        for (int r = 0; r < NB; ++r) {
+          const uint4 xv = ld_cached16(xp[r] + c);
+#pragma unroll
+          for (int j = 0; j < ROWS; ++j) acc[j][r] = dot8(wv[j][u], xv, acc[j][r]);
+        }
       }
     }
   }
 #pragma unroll
-  for (int r = 0; r < NB; ++r) acc[r] = warp_sum(acc[r]);
+  for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+    for (int r = 0; r < NB; ++r) acc[j][r] = warp_sum(acc[j][r]);
 }
 
-template <int MODE, int WPR>
-__global__ void __launch_bounds__(QKV_THREADS) qkv_sparse_kernel(QkvArgs a) {
+// A block owns RPB = (8 / WPR) * ROWS consecutive output rows j of one (head, q|k|v) pair: each group of WPR
+// warps takes ROWS of them. Every group sees the same token rows, so the block-wide barriers are uniform.
+template <int MODE, int WPR, int ROWS>
+__global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
+  pdl_prologue();
   constexpr int GROUPS = QKV_WARPS / WPR;
-  __shared__ float red[QKV_WARPS][DJV_KV_WINDOW];
+  constexpr int RPB = GROUPS * ROWS;
+  constexpr int U = (ROWS == 1) ? 8 : (ROWS == 2 ? 4 : 2);  // ROWS * U = 8 weight loads in flight per lane
+  __shared__ float red[QKV_WARPS][ROWS][8];
   __shared__ int rows_s[DJV_KV_WINDOW];
   __shared__ int nrows_s;
 
-  const int jblocks = a.hd / QKV_RPB;
+  const int jblocks = a.hd / RPB;
   const int pair = blockIdx.x / jblocks;  // i*3 + qkv
   const int jb = blockIdx.x % jblocks;
   const int i = pair / 3, qkv = pair % 3;
@@ -216,52 +234,76 @@ __global__ void __launch_bounds__(QKV_THREADS) qkv_sparse_kernel(QkvArgs a) {
   const int nchunks = a.d / 8;
   const uint4 *Xv = reinterpret_cast<const uint4 *>(a.x);
 
-  for (int jj = group; jj < QKV_RPB; jj += GROUPS) {
-    const int j = jb * QKV_RPB + jj;
-    const size_t wrow = ((size_t)qkv * a.nheads + h) * a.hd + j;
-    const uint4 *wp = reinterpret_cast<const uint4 *>(a.w + wrow * a.d);
-    const float bv = a.bias ? __half2float(a.bias[wrow]) : 0.f;
+  const int j0 = jb * RPB + group * ROWS;
+  const size_t wrow0 = ((size_t)qkv * a.nheads + h) * a.hd + j0;
+  const uint4 *wp[ROWS];
+  float bv[ROWS];
+#pragma unroll
+  for (int j = 0; j < ROWS; ++j) {
+    wp[j] = reinterpret_cast<const uint4 *>(a.w + (wrow0 + j) * a.d);
+    bv[j] = a.bias ? __half2float(a.bias[wrow0 + j]) : 0.f;
+  }
 
-    for (int r0 = 0; r0 < nrows; r0 += 4) {
-      const int nb = min(4, nrows - r0);
-      float acc[4];
-      const uint4 *xp[4];
+  constexpr int NBMAX = 8;  // token rows per pass over the weights
+  for (int r0 = 0; r0 < nrows; r0 += NBMAX) {
+    const int nb = min(NBMAX, nrows - r0);
+    float acc[ROWS][NBMAX];
+    const uint4 *xp[NBMAX];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) xp[r] = Xv + (size_t)rows_s[r0 + (r < nb ? r : 0)] * nchunks;
-      if (nb == 1) {
-        const uint4 *x1[1] = {xp[0]};
-        float a1[1];
-        multi_rowdot<1, WPR>(wp, x1, nchunks, glane, a1);
-        acc[0] = a1[0];
-      } else if (nb == 2) {
-        const uint4 *x2[2] = {xp[0], xp[1]};
-        float a2[2];
-        multi_rowdot<2, WPR>(wp, x2, nchunks, glane, a2);
-        acc[0] = a2[0];
-        acc[1] = a2[1];
-      } else {
-        multi_rowdot<4, WPR>(wp, xp, nchunks, glane, acc);
+    for (int r = 0; r < NBMAX; ++r) xp[r] = Xv + (size_t)rows_s[r0 + (r < nb ? r : 0)] * nchunks;
+    if (nb == 1) {
+      const uint4 *x1[1] = {xp[0]};
+      float a1[ROWS][1];
+      multi_rowdot<1, WPR, ROWS, U>(wp, x1, nchunks, glane, a1);
+#pragma unroll
+      for (int j = 0; j < ROWS; ++j) acc[j][0] = a1[j][0];
+    } else if (nb == 2) {
+      const uint4 *x2[2] = {xp[0], xp[1]};
+      float a2[ROWS][2];
+      multi_rowdot<2, WPR, ROWS, U>(wp, x2, nchunks, glane, a2);
+#pragma unroll
+      for (int j = 0; j < ROWS; ++j) {
+        acc[j][0] = a2[j][0];
+        acc[j][1] = a2[j][1];
       }
-      if (WPR > 1) {
-        if (lane == 0) {
+    } else if (nb <= 4) {
+      const uint4 *x4[4] = {xp[0], xp[1], xp[2], xp[3]};
+      float a4[ROWS][4];
+      multi_rowdot<4, WPR, ROWS, U>(wp, x4, nchunks, glane, a4);
 #pragma unroll
-          for (int r = 0; r < 4; ++r) red[warp][r] = acc[r];
-        }
-        // all groups run the same (jj, r0) trip counts, so this barrier is block-uniform
-        __syncthreads();
-        if (wig == 0 && lane == 0) {
+      for (int j = 0; j < ROWS; ++j)
 #pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            float s = 0.f;
+        for (int r = 0; r < 4; ++r) acc[j][r] = a4[j][r];
+    } else {
+      multi_rowdot<NBMAX, WPR, ROWS, U>(wp, xp, nchunks, glane, acc);
+    }
+    if (WPR > 1) {
+      if (lane == 0) {
 #pragma unroll
-            for (int w2 = 0; w2 < WPR; ++w2) s += red[group * WPR + w2][r];
-            acc[r] = s;
-          }
-        }
+        for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+          for (int r = 0; r < NBMAX; ++r) red[warp][j][r] = acc[j][r];
       }
+      // all groups run the same r0 trip counts, so this barrier is block-uniform
+      __syncthreads();
       if (wig == 0 && lane == 0) {
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+          for (int r = 0; r < NBMAX; ++r) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < WPR; ++w2) sum += red[group * WPR + w2][j][r];
+            acc[j][r] = sum;
+          }
+      }
+    }
+    if (wig == 0 && lane == 0) {
+#pragma unroll
+      for (int jr = 0; jr < ROWS; ++jr) {
+        const int j = j0 + jr;
         for (int r = 0; r < nb; ++r) {
-          const __half out = __float2half_rn(acc[r] + bv);
+          const __half out = __float2half_rn(acc[jr][r] + bv[jr]);
           const int row = rows_s[r0 + r];
           if (MODE == 0) {
             a.y[(((size_t)row * 3 + qkv) * a.nheads + h) * a.hd + j] = out;
@@ -276,8 +318,8 @@ __global__ void __launch_bounds__(QKV_THREADS) qkv_sparse_kernel(QkvArgs a) {
           }
         }
       }
-      if (WPR > 1) __syncthreads();
     }
+    if (WPR > 1) __syncthreads();
   }
 }
 
@@ -305,6 +347,7 @@ struct AttnArgs {
 
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
+  pdl_prologue();
   constexpr int CH = HD / 8;           // 16-byte chunks per head row
   constexpr int RPI = AT_THREADS / CH; // V rows per iteration
   __shared__ float qs[HD];
@@ -480,6 +523,7 @@ __global__ void __launch_bounds__(OP_THREADS)
 out_proj_sparse_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                        const int *__restrict__ head_idx, const int *__restrict__ n_active_dev,
                        const __half *__restrict__ bias, int d, int nheads, int nnz) {
+  pdl_prologue();
   constexpr int LPS = HD / 8;      // lanes per segment
   constexpr int SEGS = WARP / LPS; // segments per warp load
   const int tid = threadIdx.x, lane = tid % WARP;
@@ -539,6 +583,7 @@ __global__ void cache_copy_sparse_kernel(const __half *__restrict__ src, __half 
                                          const int *__restrict__ seqlen_idx,
                                          const int *__restrict__ padding, int T, int nheads, int hd,
                                          int S, long long ld_t, long long ld_h) {
+  pdl_prologue();
   const int i = blockIdx.x, t = blockIdx.y;
   const int pos0 = seqlen_idx[i * T + t];
   if (pos0 < 0) return;
@@ -566,15 +611,19 @@ static int pick_wpr(long long rows, int nchunks) {
   return wpr;
 }
 
+// `rows` = output rows expected in a typical call (heads in use x 3 x head_dim). Many rows: one warp per 4
+// weight rows (32 rows per block); fewer rows: more warps per row, down to the whole block on one row.
 template <int MODE>
-static void launch_qkv(const QkvArgs &a, int capacity_heads, int wpr, cudaStream_t st) {
-  const int grid = capacity_heads * 3 * (a.hd / QKV_RPB);
-  switch (wpr) {
-    case 1: qkv_sparse_kernel<MODE, 1><<<grid, QKV_THREADS, 0, st>>>(a); break;
-    case 2: qkv_sparse_kernel<MODE, 2><<<grid, QKV_THREADS, 0, st>>>(a); break;
-    case 4: qkv_sparse_kernel<MODE, 4><<<grid, QKV_THREADS, 0, st>>>(a); break;
-    default: qkv_sparse_kernel<MODE, 8><<<grid, QKV_THREADS, 0, st>>>(a); break;
-  }
+static void launch_qkv(const QkvArgs &a, int capacity_heads, long long rows, cudaStream_t st) {
+  const long long sms = sm_count();
+#define DJV_QKV(WPR_, ROWS_)                                                                       \
+  djv::launch_kernel(qkv_sparse_kernel<MODE, WPR_, ROWS_>,                                         \
+                     capacity_heads * 3 * (a.hd / ((QKV_WARPS / WPR_) * ROWS_)), QKV_THREADS, 0, st, a)
+  if (rows >= 32 * sms) DJV_QKV(1, 4);
+  else if (rows >= 16 * sms) DJV_QKV(2, 2);
+  else if (rows >= 8 * sms) DJV_QKV(4, 1);
+  else DJV_QKV(8, 1);
+#undef DJV_QKV
 }
 
 static int check_hd(const char *op, int hd, int d) {
@@ -601,7 +650,7 @@ extern "C" int djv_qkv_proj_sparse(void *y, const void *w, const void *x, const 
   a.y = static_cast<__half *>(y);
   a.head_idx = head_idx;
   a.batch_idx = batch_idx;
-  launch_qkv<0>(a, nnz, pick_wpr((long long)nnz * 3 * hd, d / 8), static_cast<cudaStream_t>(stream));
+  launch_qkv<0>(a, nnz, (long long)nnz * 3 * hd, static_cast<cudaStream_t>(stream));
   count_launch();
   return check_launch("qkv_proj_sparse");
 }
@@ -613,7 +662,7 @@ static int launch_out_proj(int B, __half *Y, const __half *W, const __half *X, c
   const int warps = ceil_div(d, OP_ROWS);
   const int grid = ceil_div(warps * WARP, OP_THREADS);
 #define DJV_OP(B_) \
-  out_proj_sparse_kernel<HD, B_><<<grid, OP_THREADS, 0, st>>>(Y, W, X, head_idx, n_active_dev, bias, d, nheads, nnz)
+  djv::launch_kernel(out_proj_sparse_kernel<HD, B_>, grid, OP_THREADS, 0, st, Y, W, X, head_idx, n_active_dev, bias, d, nheads, nnz)
   switch (B) {
     case 1: DJV_OP(1); break;
     case 2: DJV_OP(2); break;
@@ -662,11 +711,11 @@ static int cache_copy(bool is_k, const void *src, void *cache, const int32_t *he
   dim3 grid(nnz, T);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_k)
-    cache_copy_sparse_kernel<true><<<grid, 128, 0, st>>>(static_cast<const __half *>(src),
+    djv::launch_kernel(cache_copy_sparse_kernel<true>, grid, 128, 0, st, static_cast<const __half *>(src),
                                                          static_cast<__half *>(cache), head_idx,
                                                          seqlen_idx, padding, T, nheads, hd, S, ld_t, ld_h);
   else
-    cache_copy_sparse_kernel<false><<<grid, 128, 0, st>>>(static_cast<const __half *>(src),
+    djv::launch_kernel(cache_copy_sparse_kernel<false>, grid, 128, 0, st, static_cast<const __half *>(src),
                                                           static_cast<__half *>(cache), head_idx,
                                                           seqlen_idx, padding, T, nheads, hd, S, ld_t, ld_h);
   count_launch();
@@ -688,7 +737,7 @@ extern "C" int djv_v_cache_copy_sparse(const void *v, void *v_cache, const int32
 
 extern "C" int djv_attn_state_reset(int32_t *state, int nheads, int prompt_len, void *stream) {
   DJV_REQUIRE(state && nheads >= 1 && nheads <= 1024 && prompt_len >= 0, "attn_state_reset: bad argument");
-  attn_state_reset_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(state, nheads, prompt_len);
+  djv::launch_kernel(attn_state_reset_kernel, 1, 256, 0, static_cast<cudaStream_t>(stream), state, nheads, prompt_len);
   count_launch();
   return check_launch("attn_state_reset");
 }
@@ -718,9 +767,9 @@ static int launch_attn(AttnArgs a, int slots, int B, void *scratch, size_t scrat
     a.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + AT_COUNTER_BYTES);
   }
   dim3 grid(slots, B, nsplit);
-  if (a.hd == 128) decode_attn_kernel<128><<<grid, AT_THREADS, 0, st>>>(a);
-  else if (a.hd == 64) decode_attn_kernel<64><<<grid, AT_THREADS, 0, st>>>(a);
-  else decode_attn_kernel<32><<<grid, AT_THREADS, 0, st>>>(a);
+  if (a.hd == 128) djv::launch_kernel(decode_attn_kernel<128>, grid, AT_THREADS, 0, st, a);
+  else if (a.hd == 64) djv::launch_kernel(decode_attn_kernel<64>, grid, AT_THREADS, 0, st, a);
+  else djv::launch_kernel(decode_attn_kernel<32>, grid, AT_THREADS, 0, st, a);
   count_launch();
   return DJV_OK;
 }
@@ -743,7 +792,7 @@ extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const voi
   DJV_REQUIRE(aligned16(wqkv) && aligned16(x) && aligned16(x_ring) && aligned16(k_cache) && aligned16(v_cache),
               "attn_step: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  attn_prep_kernel<<<1, 1024, 0, st>>>(state, head_idx, head_idx ? nnz : 0, static_cast<const __half *>(x),
+  djv::launch_kernel(attn_prep_kernel, 1, 1024, 0, st, state, head_idx, head_idx ? nnz : 0, static_cast<const __half *>(x),
                                        static_cast<__half *>(x_ring), d, nheads, S);
   count_launch();
   QkvArgs a{};
@@ -757,7 +806,7 @@ extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const voi
   a.v_cache = static_cast<__half *>(v_cache);
   a.S = S;
   const int typical = head_idx ? (nnz > 0 ? nnz : 1) : nheads;
-  launch_qkv<1>(a, nheads, pick_wpr((long long)typical * 3 * hd, d / 8), st);
+  launch_qkv<1>(a, nheads, (long long)typical * 3 * hd, st);
   count_launch();
   AttnArgs t{};
   t.ctx = static_cast<__half *>(ctx);
@@ -774,7 +823,7 @@ extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const voi
 
 extern "C" int djv_attn_step_finish(int32_t *state, int nheads, void *stream) {
   DJV_REQUIRE(state && nheads >= 1, "attn_step_finish: bad argument");
-  attn_finish_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(state);
+  djv::launch_kernel(attn_finish_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), state);
   count_launch();
   return check_launch("attn_step_finish");
 }

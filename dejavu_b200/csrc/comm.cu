@@ -59,6 +59,7 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *const *
                                const __half *__restrict__ partial, const __half *residual,
                                const __half *__restrict__ gamma, const __half *__restrict__ beta,
                                int B, int d, float eps) {
+  pdl_prologue();
   __shared__ float red[LN_THREADS / WARP];
   __shared__ int failed;
   const int tid = threadIdx.x;
@@ -264,8 +265,7 @@ extern "C" int djv_allreduce_add_layernorm(djv_comm *c, void *y, void *r_out, co
               "allreduce_add_layernorm: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   c->last_stream = st;
-  allreduce_add_layernorm_kernel<<<1, LN_THREADS, 0, st>>>(
-      c->bufs_dev, c->flags_dev, c->epoch_dev, c->rank, c->world, c->slot_bytes, static_cast<__half *>(y),
+  djv::launch_kernel(allreduce_add_layernorm_kernel, 1, LN_THREADS, 0, st, c->bufs_dev, c->flags_dev, c->epoch_dev, c->rank, c->world, c->slot_bytes, static_cast<__half *>(y),
       static_cast<__half *>(r_out), static_cast<const __half *>(partial),
       static_cast<const __half *>(residual), static_cast<const __half *>(gamma),
       static_cast<const __half *>(beta), B, d, eps);

@@ -32,8 +32,36 @@ inline int env_int(const char *name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 
+// Kernel launch with programmatic dependent launch (PDL): the next kernel of a stream may be scheduled
+// while this one is still running; every kernel of this library starts with pdl_prologue(), which (1) lets
+// its own successor be scheduled early and (2) waits until all its predecessors have completed and their
+// writes are visible, before it touches any memory. Only launch latency is overlapped; ordering of data is
+// the same as without PDL. DJV_PDL=0 in the environment launches the classic way.
+bool pdl_enabled();
+
+template <typename... P, typename... A>
+inline cudaError_t launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 A &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 // ---- device side --------------------------------------------------------------------------
 constexpr int WARP = 32;
+
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 // 16-byte read-only load that does not pollute L1 (weights are streamed exactly once).
 __device__ __forceinline__ uint4 ld_stream16(const void *p) {

@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(RD_THREADS)
 rowdot_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
               const void *__restrict__ idx, const __half *__restrict__ bias, int M, int N,
               long long ldw, int idx64) {
+  pdl_prologue();
   constexpr int GROUPS = RD_WARPS / WPR;
   constexpr int GLANES = WARP * WPR;
   __shared__ float red[WPR > 1 ? RD_WARPS * ROWS * B : 1];
@@ -154,7 +155,7 @@ static void launch_rowdot(const RowdotPlan &p, __half *Y, const __half *W, const
                           const void *idx, const __half *bias, int M, int N, long long ldw,
                           int idx64, cudaStream_t st) {
 #define DJV_RD(WPR_, ROWS_)                                                               \
-  rowdot_kernel<B, ACT, WPR_, ROWS_, 4><<<p.grid, RD_THREADS, 0, st>>>(Y, W, X, idx, bias, M, N, \
+  djv::launch_kernel(rowdot_kernel<B, ACT, WPR_, ROWS_, 4>, p.grid, RD_THREADS, 0, st, Y, W, X, idx, bias, M, N, \
                                                                        ldw, idx64)
   constexpr int R = (B <= 2) ? 2 : 1;
   switch (p.wpr) {
@@ -206,6 +207,7 @@ static int rowdot_slice(int B, int act, __half *Y, const __half *W, const __half
 
 // Zero rows selected (M == 0): y = bias (or 0).
 __global__ void bias_fill_kernel(__half *Y, const __half *bias, int B, int N) {
+  pdl_prologue();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < B * N) Y[i] = bias ? bias[i % N] : __float2half(0.f);
 }
@@ -275,7 +277,7 @@ extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x,
   DJV_REQUIRE(bias == nullptr || aligned16(bias), "gather_transposed_gemv: bias must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M == 0) {
-    bias_fill_kernel<<<ceil_div(B * N, 256), 256, 0, st>>>(static_cast<__half *>(y),
+    djv::launch_kernel(bias_fill_kernel, ceil_div(B * N, 256), 256, 0, st, static_cast<__half *>(y),
                                                           static_cast<const __half *>(bias), B, N);
     count_launch();
     return check_launch("gather_transposed_gemv");

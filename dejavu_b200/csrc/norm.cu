@@ -10,6 +10,7 @@ __global__ void __launch_bounds__(LN_THREADS)
 add_layernorm_kernel(__half *__restrict__ y, __half *r_out, const __half *__restrict__ x,
                      const __half *residual, const __half *__restrict__ xbias,
                      const __half *__restrict__ gamma, const __half *__restrict__ beta, int d, float eps) {
+  pdl_prologue();
   __shared__ float red[LN_THREADS / WARP];
   const int row = blockIdx.x, tid = threadIdx.x;
   const int nchunks = d / 8;
@@ -57,8 +58,7 @@ extern "C" int djv_add_layernorm(void *y, void *r_out, const void *x, const void
                   (!r_out || aligned16(r_out)) && (!residual || aligned16(residual)) &&
                   (!xbias || aligned16(xbias)),
               "add_layernorm: pointers must be 16-byte aligned");
-  add_layernorm_kernel<<<B, LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__half *>(y), static_cast<__half *>(r_out), static_cast<const __half *>(x),
+  djv::launch_kernel(add_layernorm_kernel, B, LN_THREADS, 0, static_cast<cudaStream_t>(stream), static_cast<__half *>(y), static_cast<__half *>(r_out), static_cast<const __half *>(x),
       static_cast<const __half *>(residual), static_cast<const __half *>(xbias),
       static_cast<const __half *>(gamma), static_cast<const __half *>(beta), d, eps);
   count_launch();

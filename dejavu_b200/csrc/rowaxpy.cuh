@@ -33,6 +33,7 @@ rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __hal
                const void *__restrict__ idx, const __half *__restrict__ bias,
                float *__restrict__ partial, unsigned *__restrict__ counters, int M, int N,
                long long ldw, int idx64, int rows_per_warp) {
+  pdl_prologue();
   __shared__ __align__(16) float wsum[RA_WARPS][B][RA_COLS];
   __shared__ float tsum[B][RA_COLS];
   __shared__ float fin[RA_CLUSTER][B][RA_SLICE];
@@ -177,7 +178,8 @@ inline RowaxpyPlan plan_rowaxpy(int M, int N) {
   const int sms = sm_count();
   const int tiles = ceil_div(N / 8, WARP);
   // aim at ~2.6 blocks of 256 threads per SM
-  int mcc = (sms * 26 / 10 + tiles * RA_CLUSTER / 2) / (tiles * RA_CLUSTER);
+  static const int k_blocks_x10 = env_int("DJV_RA_BLOCKS_X10", 26);  // development knob
+  int mcc = (sms * k_blocks_x10 / 10 + tiles * RA_CLUSTER / 2) / (tiles * RA_CLUSTER);
   if (mcc < 1) mcc = 1;
   if (mcc > RA_MAX_MCC) mcc = RA_MAX_MCC;
   // no point in splitting below ~8 rows per warp
@@ -196,7 +198,7 @@ inline void launch_rowaxpy(const RowaxpyPlan &p, __half *Y, const __half *W, con
                            const void *idx, const __half *bias, float *partial, unsigned *counters,
                            int M, int N, long long ldw, int idx64, cudaStream_t st) {
   dim3 grid(p.tiles, p.mcc * RA_CLUSTER);
-  rowaxpy_kernel<B><<<grid, RA_THREADS, 0, st>>>(Y, W, X, idx, bias, partial, counters, M, N, ldw,
+  djv::launch_kernel(rowaxpy_kernel<B>, grid, RA_THREADS, 0, st, Y, W, X, idx, bias, partial, counters, M, N, ldw,
                                                  idx64, p.rpw);
 }
 

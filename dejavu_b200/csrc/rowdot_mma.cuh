@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(MM_THREADS)
 rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                   const void *__restrict__ idx, const __half *__restrict__ bias, int M, int N,
                   long long ldw, int idx64, int B) {
+  pdl_prologue();
   __shared__ float red[MM_WARPS][NT][MM_ROWS][8];
   const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
   const int g = lane / 4, t = lane % 4;
@@ -100,7 +101,7 @@ inline int launch_rowdot_mma(int act, __half *Y, const __half *W, const __half *
                              const __half *bias, int M, int N, long long ldw, int idx64, int B, cudaStream_t st) {
   const int grid = ceil_div(M, MM_ROWS);
 #define DJV_MM(ACT_) \
-  rowdot_mma_kernel<NT, ACT_><<<grid, MM_THREADS, 0, st>>>(Y, W, X, idx, bias, M, N, ldw, idx64, B)
+  djv::launch_kernel(rowdot_mma_kernel<NT, ACT_>, grid, MM_THREADS, 0, st, Y, W, X, idx, bias, M, N, ldw, idx64, B)
   switch (act) {
     case DJV_ACT_ID: DJV_MM(DJV_ACT_ID); break;
     case DJV_ACT_RELU: DJV_MM(DJV_ACT_RELU); break;

@@ -70,6 +70,7 @@ template <typename T>
 __global__ void __launch_bounds__(TK_THREADS)
 topk_kernel(int32_t *__restrict__ idx32, int64_t *__restrict__ idx64, const T *__restrict__ scores,
             int n, int K) {
+  pdl_prologue();
   using Key = typename KeyTraits<T>::Key;
   constexpr int BITS = KeyTraits<T>::BITS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -190,11 +191,11 @@ extern "C" int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int 
   if (score_is_f32) {
     e = cudaFuncSetAttribute(topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess)
-      topk_kernel<float><<<1, TK_THREADS, smem, st>>>(idx32, idx64, static_cast<const float *>(scores), n, K);
+      djv::launch_kernel(topk_kernel<float>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const float *>(scores), n, K);
   } else {
     e = cudaFuncSetAttribute(topk_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess)
-      topk_kernel<__half><<<1, TK_THREADS, smem, st>>>(idx32, idx64, static_cast<const __half *>(scores), n, K);
+      djv::launch_kernel(topk_kernel<__half>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const __half *>(scores), n, K);
   }
   if (e != cudaSuccess) {
     set_error("topk: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
