@@ -108,31 +108,52 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *const *
   for (int row = 0; row < B; ++row) {
     const size_t off = (size_t)row * d;
     float vals[LN_MAX_CHUNKS][8];
+    // All peers' pieces of two chunks are requested before the first one is used: one NVLink round trip per
+    // pair of chunks instead of one per peer.
+    constexpr int G = 2;
 #pragma unroll
-    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
-      const int ch = c * LN_THREADS + tid;
-      if (ch < nchunks) {
-        float f[8], t[8];
+    for (int c0 = 0; c0 < LN_MAX_CHUNKS; c0 += G) {
+      uint4 v[G][AR_MAX_WORLD];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = 0.f;
-        for (int p = 0; p < world; ++p) {
-          const char *src = static_cast<const char *>(bufs[p]) + slot_off + (off + (size_t)ch * 8) * 2;
-          unpack8(ld_peer16(src), t);
+      for (int g = 0; g < G; ++g) {
+        const int ch = (c0 + g) * LN_THREADS + tid;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] += t[e];
+        for (int p = 0; p < AR_MAX_WORLD; ++p) {
+          if (ch < nchunks && p < world) {
+            const char *src = static_cast<const char *>(bufs[p]) + slot_off + (off + (size_t)ch * 8) * 2;
+            v[g][p] = ld_peer16(src);
+          } else {
+            v[g][p] = make_uint4(0, 0, 0, 0);
+          }
         }
-        round_store8(f, nullptr);  // the all-reduced activation is an fp16 tensor
-        if (residual) {
-          unpack8(*reinterpret_cast<const uint4 *>(residual + off + (size_t)ch * 8), t);
+      }
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] += t[e];
+      for (int g = 0; g < G; ++g) {
+        const int c = c0 + g;
+        const int ch = c * LN_THREADS + tid;
+        if (ch < nchunks) {
+          float f[8], t[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = 0.f;
+#pragma unroll
+          for (int p = 0; p < AR_MAX_WORLD; ++p) {  // rank order; absent ranks hold zeros
+            unpack8(v[g][p], t);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] += t[e];
+          }
+          round_store8(f, nullptr);  // the all-reduced activation is an fp16 tensor
+          if (residual) {
+            unpack8(*reinterpret_cast<const uint4 *>(residual + off + (size_t)ch * 8), t);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] += t[e];
+          }
+          round_store8(f, r_out ? r_out + off + (size_t)ch * 8 : nullptr);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) vals[c][e] = f[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) vals[c][e] = 0.f;
         }
-        round_store8(f, r_out ? r_out + off + (size_t)ch * 8 : nullptr);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) vals[c][e] = f[e];
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) vals[c][e] = 0.f;
       }
     }
     layernorm_store(vals, nchunks, d, gamma, beta, eps, y + off, red);
