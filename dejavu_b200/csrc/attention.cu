@@ -541,20 +541,33 @@ out_proj_sparse_kernel(__half *__restrict__ Y, const __half *__restrict__ W, con
 #pragma unroll
     for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
 
-  for (int i = seg; i < n_eff; i += SEGS) {
-    const int h = head_idx[i];
-    uint4 wv[OP_ROWS];
+  // two head segments per lane and iteration: 2 * OP_ROWS independent 16-byte loads in flight
+  for (int i0 = seg; i0 < n_eff; i0 += SEGS * 2) {
+    int h[2];
+    bool ok[2];
+    uint4 wv[2][OP_ROWS];
 #pragma unroll
-    for (int r = 0; r < OP_ROWS; ++r) {
-      const int n = n0 + r;
-      wv[r] = (n < d) ? ld_stream16(W + (size_t)n * row_stride + (size_t)h * HD + c * 8)
-                      : make_uint4(0, 0, 0, 0);
+    for (int k = 0; k < 2; ++k) {
+      const int i = i0 + k * SEGS;
+      ok[k] = i < n_eff;
+      h[k] = ok[k] ? head_idx[i] : 0;
+#pragma unroll
+      for (int r = 0; r < OP_ROWS; ++r) {
+        const int n = n0 + r;
+        wv[k][r] = (ok[k] && n < d) ? ld_stream16(W + (size_t)n * row_stride + (size_t)h[k] * HD + c * 8)
+                                    : make_uint4(0, 0, 0, 0);
+      }
     }
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-      const uint4 xv = ld_cached16(X + ((size_t)b * nheads + h) * HD + c * 8);
+    for (int k = 0; k < 2; ++k) {
+      if (ok[k]) {
 #pragma unroll
-      for (int r = 0; r < OP_ROWS; ++r) acc[r][b] = dot8(wv[r], xv, acc[r][b]);
+        for (int b = 0; b < B; ++b) {
+          const uint4 xv = ld_cached16(X + ((size_t)b * nheads + h[k]) * HD + c * 8);
+#pragma unroll
+          for (int r = 0; r < OP_ROWS; ++r) acc[r][b] = dot8(wv[k][r], xv, acc[r][b]);
+        }
+      }
     }
   }
 #pragma unroll
