@@ -274,8 +274,14 @@ extern "C" int djv_gather_gemv(void *y, const void *w, const void *x, const void
 
 extern "C" size_t djv_gather_transposed_gemv_scratch_bytes(int B, int N, int M) {
   if (B < 1 || N < 8 || M < 0) return 0;
+  // a call is cut into slices of up to 4 rows of x, and the plan depends on the slice's row count
   const int bs = B < 4 ? B : 4;
-  return rowaxpy_scratch_bytes(bs, N, M);
+  size_t need = 0;
+  for (int b = 1; b <= bs; ++b) {
+    const size_t n = rowaxpy_scratch_bytes(b, N, M);
+    if (n > need) need = n;
+  }
+  return need;
 }
 
 extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x, const void *idx,

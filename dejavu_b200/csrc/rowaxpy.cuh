@@ -1,11 +1,11 @@
 // rowaxpy:  y[b,:] = sum_m x[b,m] * w[idx[m],:] + bias    (gather transposed GEMV, fc2 / out_proj shape)
 //
 // grid = (column tiles, 8*MCC), thread-block clusters of 8 along y.
-//   * a block owns 256 consecutive columns (32 lanes x one 16-byte chunk) and its 8 warps own
+//   * a block owns 256*CW consecutive columns (32 lanes x CW 16-byte chunks, 512 B apart) and its 8 warps own
 //     disjoint slices of the index list: a warp streams its rows with 8 independent 128-bit loads in
-//     flight per lane and keeps 8*B fp32 sums per lane;
+//     flight per lane (8/CW rows x CW chunks) and keeps 8*CW*B fp32 sums per lane;
 //   * the 8 warp sums are added through shared memory, the 8 blocks of a cluster through distributed
-//     shared memory (plain ld.shared::cluster, each block finishing 32 of the 256 columns);
+//     shared memory (plain ld.shared::cluster, each block finishing an eighth of the tile's columns);
 //   * with MCC > 1 clusters per column tile the per-cluster sums go to `partial` and the last block to
 //     arrive adds them in cluster order. Every sum has a fixed order: results are deterministic.
 // Scratch: [4096 B of zeroed counters][MCC * B * N floats]. The kernel leaves the counters at zero.
@@ -20,20 +20,22 @@ namespace cg = cooperative_groups;
 
 constexpr int RA_THREADS = 256;
 constexpr int RA_WARPS = RA_THREADS / WARP;
-constexpr int RA_COLS = WARP * 8;  // columns per block
 constexpr int RA_CLUSTER = 8;
-constexpr int RA_SLICE = RA_COLS / RA_CLUSTER;  // columns a block finishes
-constexpr int RA_MAX_MCC = 4;
+constexpr int RA_MAX_MCC = 6;
 constexpr int RA_COUNTER_BYTES = 4096;
 constexpr int RA_MAX_B = 4;
 
-template <int B>
+// CW: 16-byte chunks per lane along a row; a warp reads CW*512 contiguous bytes of every row it visits
+template <int B, int CW>
 __global__ void __cluster_dims__(1, RA_CLUSTER, 1) __launch_bounds__(RA_THREADS)
 rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                const void *__restrict__ idx, const __half *__restrict__ bias,
                float *__restrict__ partial, unsigned *__restrict__ counters, int M, int N,
                long long ldw, int idx64, int rows_per_warp) {
   pdl_prologue();
+  constexpr int RA_COLS = WARP * 8 * CW;           // columns per block
+  constexpr int RA_SLICE = RA_COLS / RA_CLUSTER;   // columns a block finishes
+  constexpr int U = 8 / CW;                        // rows in flight per lane: U * CW = 8 loads
   __shared__ __align__(16) float wsum[RA_WARPS][B][RA_COLS];
   __shared__ float tsum[B][RA_COLS];
   __shared__ float fin[RA_CLUSTER][B][RA_SLICE];
@@ -45,23 +47,24 @@ rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __hal
   const int crank = blockIdx.y % RA_CLUSTER;  // rank inside the cluster
   const int mcc = blockIdx.y / RA_CLUSTER, MCC = gridDim.y / RA_CLUSTER;
   const int nchunks = N / 8;
-  const int chunk = tile * WARP + lane;
-  const bool active = chunk < nchunks;
+  const int chunk0 = tile * WARP * CW + lane;  // this lane's chunks: chunk0 + c*32
 
   const int wslot = blockIdx.y * RA_WARPS + warp;
   const int m_begin = min(M, wslot * rows_per_warp);
   const int m_end = min(M, m_begin + rows_per_warp);
 
-  float acc[B][8];
+  float acc[B][CW][8];
 #pragma unroll
   for (int b = 0; b < B; ++b)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[b][e] = 0.f;
+    for (int c = 0; c < CW; ++c)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[b][c][e] = 0.f;
 
-  const __half *wcol = W + (size_t)chunk * 8;
-  constexpr int U = 8;
+  const __half *wcol = W + (size_t)chunk0 * 8;
   for (int i0 = m_begin; i0 < m_end; i0 += WARP) {
     // lane l holds row i0+l of this warp's slice: its index and its x values
+    // (fetching these further ahead of the weight stream was measured slower)
     const int mi = i0 + lane;
     int my_row = 0;
     float my_x[B];
@@ -74,30 +77,38 @@ rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __hal
     }
     const int cnt = min(WARP, m_end - i0);
     for (int u0 = 0; u0 < cnt; u0 += U) {
-      uint4 wv[U];
+      uint4 wv[U][CW];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int r = __shfl_sync(0xffffffffu, my_row, (u0 + u) & 31);
-        if (active && u0 + u < cnt)
-          wv[u] = ld_stream16(wcol + (long long)r * ldw);
-        else
-          wv[u] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+          if (chunk0 + c * WARP < nchunks && u0 + u < cnt)
+            wv[u][c] = ld_stream16(wcol + (long long)r * ldw + c * WARP * 8);
+          else
+            wv[u][c] = make_uint4(0, 0, 0, 0);
+        }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const float2 w0 = h2f(wv[u].x), w1 = h2f(wv[u].y), w2 = h2f(wv[u].z), w3 = h2f(wv[u].w);
+        float xb[B];
+        // rows past the end of the slice carry x = 0 and zero weights
 #pragma unroll
-        for (int b = 0; b < B; ++b) {
-          // rows past the end of the slice carry x = 0 and zero weights
-          const float xb = __shfl_sync(0xffffffffu, my_x[b], (u0 + u) & 31);
-          acc[b][0] = fmaf(xb, w0.x, acc[b][0]);
-          acc[b][1] = fmaf(xb, w0.y, acc[b][1]);
-          acc[b][2] = fmaf(xb, w1.x, acc[b][2]);
-          acc[b][3] = fmaf(xb, w1.y, acc[b][3]);
-          acc[b][4] = fmaf(xb, w2.x, acc[b][4]);
-          acc[b][5] = fmaf(xb, w2.y, acc[b][5]);
-          acc[b][6] = fmaf(xb, w3.x, acc[b][6]);
-          acc[b][7] = fmaf(xb, w3.y, acc[b][7]);
+        for (int b = 0; b < B; ++b) xb[b] = __shfl_sync(0xffffffffu, my_x[b], (u0 + u) & 31);
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+          const float2 w0 = h2f(wv[u][c].x), w1 = h2f(wv[u][c].y), w2 = h2f(wv[u][c].z), w3 = h2f(wv[u][c].w);
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            acc[b][c][0] = fmaf(xb[b], w0.x, acc[b][c][0]);
+            acc[b][c][1] = fmaf(xb[b], w0.y, acc[b][c][1]);
+            acc[b][c][2] = fmaf(xb[b], w1.x, acc[b][c][2]);
+            acc[b][c][3] = fmaf(xb[b], w1.y, acc[b][c][3]);
+            acc[b][c][4] = fmaf(xb[b], w2.x, acc[b][c][4]);
+            acc[b][c][5] = fmaf(xb[b], w2.y, acc[b][c][5]);
+            acc[b][c][6] = fmaf(xb[b], w3.x, acc[b][c][6]);
+            acc[b][c][7] = fmaf(xb[b], w3.y, acc[b][c][7]);
+          }
         }
       }
     }
@@ -105,23 +116,29 @@ rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __hal
 
   // 8 warps -> block
 #pragma unroll
-  for (int b = 0; b < B; ++b) {
-    float4 *dst = reinterpret_cast<float4 *>(&wsum[warp][b][lane * 8]);
-    dst[0] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
-    dst[1] = make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]);
-  }
+  for (int b = 0; b < B; ++b)
+#pragma unroll
+    for (int c = 0; c < CW; ++c) {
+      float4 *dst = reinterpret_cast<float4 *>(&wsum[warp][b][(c * WARP + lane) * 8]);
+      dst[0] = make_float4(acc[b][c][0], acc[b][c][1], acc[b][c][2], acc[b][c][3]);
+      dst[1] = make_float4(acc[b][c][4], acc[b][c][5], acc[b][c][6], acc[b][c][7]);
+    }
   __syncthreads();
 #pragma unroll
-  for (int b = 0; b < B; ++b) {
-    float s = 0.f;
+  for (int b = 0; b < B; ++b)
 #pragma unroll
-    for (int w2 = 0; w2 < RA_WARPS; ++w2) s += wsum[w2][b][tid];
-    tsum[b][tid] = s;
-  }
+    for (int c = 0; c < CW; ++c) {
+      float s = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < RA_WARPS; ++w2) s += wsum[w2][b][c * RA_THREADS + tid];
+      tsum[b][c * RA_THREADS + tid] = s;
+    }
   // 8 blocks -> cluster: block `crank` finishes columns [crank*32, crank*32+32) of the tile
   cluster.sync();
-  {
-    const int src = tid / RA_SLICE, col = tid % RA_SLICE;
+#pragma unroll
+  for (int c = 0; c < CW; ++c) {
+    const int e = c * RA_THREADS + tid;
+    const int src = e / RA_SLICE, col = e % RA_SLICE;
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       const float *remote = cluster.map_shared_rank(&tsum[b][crank * RA_SLICE + col], src);
@@ -171,25 +188,71 @@ rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __hal
 }
 
 struct RowaxpyPlan {
-  int tiles, mcc, rpw;
+  int tiles, mcc, rpw, cw;
 };
 
-inline RowaxpyPlan plan_rowaxpy(int M, int N) {
-  const int sms = sm_count();
-  const int tiles = ceil_div(N / 8, WARP);
-  // aim at ~2.6 blocks of 256 threads per SM
-  static const int k_blocks_x10 = env_int("DJV_RA_BLOCKS_X10", 26);  // development knob
-  int mcc = (sms * k_blocks_x10 / 10 + tiles * RA_CLUSTER / 2) / (tiles * RA_CLUSTER);
+// Clusters of rowaxpy_kernel<B, CW> the device can hold at once (all GPCs together); 0 if the query fails.
+template <int B, int CW>
+inline int rowaxpy_query_clusters() {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, RA_CLUSTER, 1);
+  cfg.blockDim = dim3(RA_THREADS, 1, 1);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = RA_CLUSTER;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, rowaxpy_kernel<B, CW>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+// B in 1..4; cw as chosen by rowaxpy_chunks_per_lane(B). Cached: all devices of a process are the same model.
+inline int rowaxpy_max_clusters(int B, int cw) {
+  static int cache[RA_MAX_B + 1] = {0, 0, 0, 0, 0};
+  if (B < 1 || B > RA_MAX_B) return 0;
+  if (cache[B] == 0) {
+    int n = 0;
+    if (cw == 2) n = (B == 1) ? rowaxpy_query_clusters<1, 2>() : rowaxpy_query_clusters<2, 2>();
+    else if (B == 1) n = rowaxpy_query_clusters<1, 1>();
+    else if (B == 2) n = rowaxpy_query_clusters<2, 1>();
+    else if (B == 3) n = rowaxpy_query_clusters<3, 1>();
+    else n = rowaxpy_query_clusters<4, 1>();
+    // fall-back: 2 blocks per multiprocessor, less what the cluster granularity of a GPC loses
+    cache[B] = n > 0 ? n : (sm_count() * 2) / RA_CLUSTER * 7 / 8;
+  }
+  return cache[B];
+}
+
+// 16-byte chunks per lane: 1 KB contiguous per row and warp (measured faster than 512 B at equal grids)
+// where the shared-memory reduction buffers still fit statically
+inline int rowaxpy_chunks_per_lane(int B) {
+  static const int k_cw = env_int("DJV_RA_CW", 2);  // development knob
+  return (k_cw >= 2 && B <= 2) ? 2 : 1;
+}
+
+// One wave: as many clusters per column tile as the device holds at once. A grid that spills into a second,
+// partly filled wave was measured 20-40% slower than a smaller grid that fits.
+inline RowaxpyPlan plan_rowaxpy(int M, int N, int B) {
+  const int cw = rowaxpy_chunks_per_lane(B);
+  const int tiles = ceil_div(N / 8, WARP * cw);
+  static const int k_mcc = env_int("DJV_RA_MCC", 0);  // development knob
+  int mcc = k_mcc > 0 ? k_mcc : rowaxpy_max_clusters(B, cw) / tiles;
   if (mcc < 1) mcc = 1;
   if (mcc > RA_MAX_MCC) mcc = RA_MAX_MCC;
   // no point in splitting below ~8 rows per warp
   while (mcc > 1 && ceil_div(M, mcc * RA_CLUSTER * RA_WARPS) < 8) --mcc;
   const int rpw = ceil_div(M, mcc * RA_CLUSTER * RA_WARPS);
-  return {tiles, mcc, rpw < 1 ? 1 : rpw};
+  return {tiles, mcc, rpw < 1 ? 1 : rpw, cw};
 }
 
 inline size_t rowaxpy_scratch_bytes(int B, int N, int M) {
-  const RowaxpyPlan p = plan_rowaxpy(M, N);
+  const RowaxpyPlan p = plan_rowaxpy(M, N, B);
   return RA_COUNTER_BYTES + (size_t)p.mcc * B * N * sizeof(float);
 }
 
@@ -198,15 +261,19 @@ inline void launch_rowaxpy(const RowaxpyPlan &p, __half *Y, const __half *W, con
                            const void *idx, const __half *bias, float *partial, unsigned *counters,
                            int M, int N, long long ldw, int idx64, cudaStream_t st) {
   dim3 grid(p.tiles, p.mcc * RA_CLUSTER);
-  djv::launch_kernel(rowaxpy_kernel<B>, grid, RA_THREADS, 0, st, Y, W, X, idx, bias, partial, counters, M, N, ldw,
-                                                 idx64, p.rpw);
+  if (p.cw == 2 && B <= 2)
+    djv::launch_kernel(rowaxpy_kernel<(B <= 2 ? B : 1), 2>, grid, RA_THREADS, 0, st, Y, W, X, idx, bias, partial,
+                       counters, M, N, ldw, idx64, p.rpw);
+  else
+    djv::launch_kernel(rowaxpy_kernel<B, 1>, grid, RA_THREADS, 0, st, Y, W, X, idx, bias, partial, counters, M, N,
+                       ldw, idx64, p.rpw);
 }
 
 // B <= RA_MAX_B rows of x per launch
 inline int rowaxpy_slice(int B, __half *Y, const __half *W, const __half *X, const void *idx,
                          const __half *bias, void *scratch, int M, int N, long long ldw, int idx64,
                          cudaStream_t st) {
-  const RowaxpyPlan p = plan_rowaxpy(M, N);
+  const RowaxpyPlan p = plan_rowaxpy(M, N, B);
   if ((size_t)p.tiles * RA_CLUSTER * sizeof(unsigned) > RA_COUNTER_BYTES) {
     set_error("gather_transposed_gemv: N=%d needs more block counters than the scratch header holds", N);
     return DJV_ERR_UNSUPPORTED;

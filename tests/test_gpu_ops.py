@@ -269,9 +269,12 @@ def test_topk_special_values(cuda):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("nheads,hd,d,T_,nnz", [(12, 128, 12288, 16, 4), (9, 128, 9216, 1, 3), (32, 128, 4096, 5, 12),
                                                  (8, 64, 512, 16, 8), (4, 32, 256, 3, 1)])
-def test_qkv_proj_sparse_vs_oracle(cuda, nheads, hd, d, T_, nnz):
+@pytest.mark.parametrize("rpb", [0, 32, 8, 2])  # 0: the library's own choice; 32 and 8 have the tensor-core path
+def test_qkv_proj_sparse_vs_oracle(cuda, monkeypatch, nheads, hd, d, T_, nnz, rpb):
     from dejavu_b200 import ops
 
+    if rpb:
+        monkeypatch.setenv("DJV_QKV_RPB", str(rpb))
     gen = torch.Generator().manual_seed(nheads * d)
     W, b = rand(gen, (3, nheads, hd, d), 0.02), rand(gen, (3, nheads, hd), 0.1)
     x = rand(gen, (T_, d))
@@ -339,9 +342,12 @@ def test_add_layernorm_vs_oracle(cuda, B, d):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("nheads,hd,d,P,steps,nsel", [(6, 32, 256, 5, 37, 2), (12, 128, 1536, 40, 35, 4),
                                                        (9, 128, 1152, 130, 20, 3)])
-def test_attn_step_state_machine_vs_oracle(cuda, nheads, hd, d, P, steps, nsel):
+@pytest.mark.parametrize("rpb", [0, 32, 8])  # rows per block of the QKV kernel; 32 and 8 back-fill on tensor cores
+def test_attn_step_state_machine_vs_oracle(cuda, monkeypatch, nheads, hd, d, P, steps, nsel, rpb):
     from dejavu_b200 import _lib
 
+    if rpb:
+        monkeypatch.setenv("DJV_QKV_RPB", str(rpb))
     lib = _lib.load()
     gen = torch.Generator().manual_seed(nheads + P)
     S = P + steps + 8
