@@ -728,14 +728,16 @@ static int pick_wpr(long long rows, int nchunks) {
 template <int MODE>
 static void launch_qkv(QkvArgs a, int capacity_heads, long long rows, cudaStream_t st) {
   const long long sms = sm_count();
-  // development knobs, read at every launch: DJV_QKV_MMA_MIN (token rows from which a pair takes the
-  // tensor-core path; 17 switches it off) and DJV_QKV_RPB (32, 8, 2 or 1: force the rows-per-block variant)
-  a.mma_min_rows = env_int("DJV_QKV_MMA_MIN", 3);
+  // development knobs, read at every launch: DJV_QKV_RPB (32, 8, 2 or 1: force the rows-per-block variant)
+  // and DJV_QKV_MMA_MIN (token rows from which a pair takes the tensor-core path; 17 switches it off)
   const int force = env_int("DJV_QKV_RPB", 0);
   if (force == 32 && a.hd % 32 == 0) rows = 32 * sms;
   else if (force == 8) rows = 16 * sms;
   else if (force == 2) rows = 8 * sms;
   else if (force == 1) rows = 0;
+  // full 16-row tiles stream faster than the CUDA-core path even for a single token row (measured);
+  // the half-filled tiles of the 8-rows-per-block variant only pay from three token rows on
+  a.mma_min_rows = env_int("DJV_QKV_MMA_MIN", rows >= 32 * sms ? 1 : 3);
 #define DJV_QKV(WPR_, ROWS_)                                                                       \
   djv::launch_kernel(qkv_sparse_kernel<MODE, WPR_, ROWS_>,                                         \
                      capacity_heads * 3 * (a.hd / ((QKV_WARPS / WPR_) * ROWS_)), QKV_THREADS, 0, st, a)
@@ -899,11 +901,11 @@ extern "C" size_t djv_attn_step_scratch_bytes(int nheads, int hd, int S) {
   return attn_scratch_bytes(nheads, 1, hd, S);
 }
 
-extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, const void *x,
-                             void *x_ring, void *k_cache, void *v_cache, int32_t *state,
-                             const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
-                             float softmax_scale, void *scratch, size_t scratch_bytes, void *stream) {
-  DJV_REQUIRE(ctx && q_out && wqkv && x && x_ring && k_cache && v_cache && state, "attn_step: null pointer");
+extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x,
+                                     void *x_ring, void *k_cache, void *v_cache, int32_t *state,
+                                     const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
+                                     void *stream) {
+  DJV_REQUIRE(q_out && wqkv && x && x_ring && k_cache && v_cache && state, "attn_step: null pointer");
   int rc = check_hd("attn_step", hd, d);
   if (rc) return rc;
   DJV_REQUIRE(nheads >= 1 && nheads <= 1024, "attn_step: nheads=%d outside [1,1024]", nheads);
@@ -928,17 +930,40 @@ extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const voi
   const int typical = head_idx ? (nnz > 0 ? nnz : 1) : nheads;
   launch_qkv<1>(a, nheads, (long long)typical * 3 * hd, st);
   count_launch();
+  return check_launch("attn_step_project");
+}
+
+extern "C" int djv_attn_step_attend(void *ctx, const void *q, const void *k_cache, const void *v_cache,
+                                    int32_t *state, int nheads, int hd, int S, float softmax_scale,
+                                    void *scratch, size_t scratch_bytes, void *stream) {
+  DJV_REQUIRE(ctx && q && k_cache && v_cache && state, "attn_step: null pointer");
+  DJV_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attn_step: head_dim %d not in {32,64,128}", hd);
+  DJV_REQUIRE(nheads >= 1 && nheads <= 1024, "attn_step: nheads=%d outside [1,1024]", nheads);
+  DJV_REQUIRE(S >= 1, "attn_step: cache capacity S=%d", S);
+  DJV_REQUIRE(aligned16(k_cache) && aligned16(v_cache), "attn_step: pointers must be 16-byte aligned");
   AttnArgs t{};
   t.ctx = static_cast<__half *>(ctx);
-  t.q = static_cast<const __half *>(q_out);
-  t.k_cache = a.k_cache;
-  t.v_cache = a.v_cache;
+  t.q = static_cast<const __half *>(q);
+  t.k_cache = static_cast<const __half *>(k_cache);
+  t.v_cache = static_cast<const __half *>(v_cache);
   t.state = state;
   t.nnz = nheads; t.nheads = nheads; t.hd = hd; t.S = S; t.len = 0;
   t.scale = softmax_scale;
-  rc = launch_attn(t, nheads, 1, scratch, scratch_bytes, st, "attn_step");
+  int rc = launch_attn(t, nheads, 1, scratch, scratch_bytes, static_cast<cudaStream_t>(stream), "attn_step");
   if (rc) return rc;
-  return check_launch("attn_step");
+  return check_launch("attn_step_attend");
+}
+
+extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, const void *x,
+                             void *x_ring, void *k_cache, void *v_cache, int32_t *state,
+                             const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
+                             float softmax_scale, void *scratch, size_t scratch_bytes, void *stream) {
+  DJV_REQUIRE(ctx != nullptr, "attn_step: null pointer");
+  int rc = djv_attn_step_project(q_out, wqkv, bqkv, x, x_ring, k_cache, v_cache, state, head_idx, nnz, d, nheads,
+                                 hd, S, stream);
+  if (rc) return rc;
+  return djv_attn_step_attend(ctx, q_out, k_cache, v_cache, state, nheads, hd, S, softmax_scale, scratch,
+                              scratch_bytes, stream);
 }
 
 extern "C" int djv_attn_step_finish(int32_t *state, int nheads, void *stream) {

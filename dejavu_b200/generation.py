@@ -14,6 +14,7 @@ for every step; only input_ids and position_ids are rewritten between replays.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from types import SimpleNamespace
@@ -117,7 +118,10 @@ def update_graph_cache(model, cache, batch_size, seqlen_og, max_seqlen, tensor_p
     from . import _lib
 
     launches_before = _lib.launch_count()
-    with torch.cuda.graph(graph):
+    # captured on a high-priority stream: when a main-chain kernel and look-ahead work on a side stream both
+    # have blocks waiting for a multiprocessor, the main chain goes first
+    priority = int(os.environ.get("DJV_MAIN_PRIORITY", "-1"))  # development knob; 0 = same as the side streams
+    with torch.cuda.graph(graph, stream=torch.cuda.Stream(device=device, priority=priority)):
         step()
     cache.launches_per_step = _lib.launch_count() - launches_before  # kernels of libdejavu_b200 per replay
     cache.graph = graph

@@ -381,7 +381,9 @@ class ParallelMHASparseAttMlp(nn.Module):
         return ctx.transpose(1, 2).reshape(B, L, n * hd)
 
     # ---- decode step ---------------------------------------------------------------------------
-    def _decode_attention(self, x, head_idx, inference_params):
+    def _decode_attention(self, x, head_idx, inference_params, between=None):
+        """One decode step of this layer's attention; `between()` is called after the projection kernels are
+        queued and before the attention kernel (the place to fork look-ahead work onto a side stream)."""
         n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
         assert x.size(0) == 1, "the sparse decode path keeps one sequence (mha_dejavu.py:1318, 1469)"
         k_cache, v_cache = inference_params.key_value_memory_dict[self.layer_idx]
@@ -395,10 +397,15 @@ class ParallelMHASparseAttMlp(nn.Module):
             head_idx = head_idx.contiguous()
             nnz = head_idx.numel()
         bias = self.Wqkv.bias
-        call("djv_attn_step", b["ctx"].data_ptr(), b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
+        call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
              None if bias is None else bias.data_ptr(), xf.data_ptr(), b["x_ring"].data_ptr(), k_cache.data_ptr(),
              v_cache.data_ptr(), b["state"].data_ptr(), None if head_idx is None else head_idx.data_ptr(), nnz, d, n,
-             hd, S, float(self.softmax_scale), b["scratch"].data_ptr(), b["scratch"].numel(), st)
+             hd, S, st)
+        if between is not None:
+            between()
+        call("djv_attn_step_attend", b["ctx"].data_ptr(), b["q"].data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+             b["state"].data_ptr(), n, hd, S, float(self.softmax_scale), b["scratch"].data_ptr(),
+             b["scratch"].numel(), st)
         out = torch.empty(1, d, dtype=x.dtype, device=x.device)
         ob = self.out_proj.bias
         state = b["state"]
@@ -414,27 +421,34 @@ class ParallelMHASparseAttMlp(nn.Module):
         decoding = inference_params is not None and inference_params.sequence_len_offset > 0
         # Look-ahead work runs beside the attention, as in the reference (sp_stream, mha_dejavu.py:1364-1370,
         # 1501-1510): the MLP top-K continues on the stream that produced the logits, the head predictor
-        # forks from here; consumers wait on the event attached to each result.
+        # forks from the main stream; consumers wait on the event attached to each result.
         mlp_idx = None
         if mlp_sp_logit is not None:
             with _side(x, "mlp", after=mlp_sp_logit) as done:
                 mlp_idx = ops.topk_indices(mlp_sp_logit, self.mlp_k, torch.int32)
                 done(mlp_idx)
-        att_idx = None
-        if do_token_generation and self.sp is not None and self.run_predictor:
-            with _side(x, "att", after=residual) as done:
-                att_idx = ops.topk_indices(self.sp(residual), self.att_k, torch.int32)
-                done(att_idx)
+        result = {"att_idx": None}
+
+        def predict_heads():
+            if do_token_generation and self.sp is not None and self.run_predictor:
+                with _side(x, "att", after=residual) as done:
+                    result["att_idx"] = ops.topk_indices(self.sp(residual), self.att_k, torch.int32)
+                    done(result["att_idx"])
+
         if decoding:
             assert do_token_generation
             _wait_ready(head_idx)
-            out = self._decode_attention(x, head_idx if self.sparse_attention else None, inference_params)
+            # the head predictor forks after the QKV projection: its GEMVs then overlap the attention kernel,
+            # which leaves HBM mostly idle, instead of taking the multiprocessors just before the projection
+            out = self._decode_attention(x, head_idx if self.sparse_attention else None, inference_params,
+                                         between=predict_heads)
         else:
+            predict_heads()
             out = self.out_proj(self._prompt_attention(x, inference_params))
         if not self.skip_all_reduce:
             out = all_reduce(out, self.process_group)
         _wait_ready(mlp_idx)  # this layer's MLP is next on the main stream
-        return out, mlp_idx, att_idx
+        return out, mlp_idx, result["att_idx"]
 
 
 class ParallelMHADejavu(ParallelMHASparseAttMlp):

@@ -191,6 +191,15 @@ int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, co
                   void *x_ring, void *k_cache, void *v_cache, int32_t *state,
                   const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
                   float softmax_scale, void *scratch, size_t scratch_bytes, void *stream);
+/* The same step as two calls, for a caller that wants to fork other work onto a second stream between the
+ * projection and the attention (the look-ahead head predictor, mha_dejavu.py:1364-1370):
+ * djv_attn_step_project = steps 1-2, djv_attn_step_attend = step 3 (q = the q_out of the first call). */
+int djv_attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x, void *x_ring,
+                          void *k_cache, void *v_cache, int32_t *state, const int32_t *head_idx, int nnz,
+                          int d, int nheads, int hd, int S, void *stream);
+int djv_attn_step_attend(void *ctx, const void *q, const void *k_cache, const void *v_cache, int32_t *state,
+                         int nheads, int hd, int S, float softmax_scale, void *scratch, size_t scratch_bytes,
+                         void *stream);
 int djv_attn_step_finish(int32_t *state, int nheads, void *stream);
 
 /* Single-query attention over the caches for an explicit head list (no lazy state):
