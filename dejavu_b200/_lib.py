@@ -58,7 +58,8 @@ SIGNATURES = {
     "djv_ipc_get_handle": (_i, [_vp, C.c_char_p]),
     "djv_ipc_open": (_i, [C.c_char_p, C.POINTER(_vp)]),
     "djv_ipc_close": (_i, [_vp]),
-    "djv_comm_create": (_i, [C.POINTER(_vp), _i, _i, C.POINTER(_vp), C.POINTER(_vp), _sz, _i]),
+    "djv_comm_buffer_bytes": (_sz, [_i, _sz]),
+    "djv_comm_create": (_i, [C.POINTER(_vp), _i, _i, C.POINTER(_vp), _sz]),
     "djv_comm_destroy": (_i, [_vp]),
     "djv_comm_status": (_i, [_vp]),
     "djv_allreduce_add_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),

@@ -3,8 +3,8 @@
 Replaces the NCCL all_reduce after out_proj and after fc2 (Dejavu/src/models/modules/mha_dejavu.py:1498,
 Dejavu/src/ops/fused_dense_sparse_dejavu.py:937-940) plus the add + norm that follows it in the block
 (Dejavu/src/models/modules/block_dejavu.py:575-584, 625-636). torch.distributed is only used to exchange
-the CUDA IPC handles at set-up; the data path is the kernel in csrc/comm.cu reading the peers' buffers
-with plain loads over NVLink.
+the CUDA IPC handles at set-up; the data path is the kernel in csrc/comm.cu storing each rank's partial
+into the peers' receive buffers with plain stores over NVLink.
 """
 from __future__ import annotations
 
@@ -18,40 +18,35 @@ from ._lib import call
 
 
 class TensorParallelComm:
-    SLOTS = 2
-    FLAG_BYTES = 256
-
     def __init__(self, process_group, device, max_bytes: int):
         self.pg = process_group
         self.rank, self.world = process_group.rank(), process_group.size()
         self.device = device
         lib = _lib.load()
         self.slot_bytes = (max_bytes + 255) // 256 * 256
-        buf, flags = C.c_void_p(), C.c_void_p()
-        _lib.check("djv_ipc_alloc", lib.djv_ipc_alloc(self.slot_bytes * self.SLOTS, C.byref(buf)))
-        _lib.check("djv_ipc_alloc", lib.djv_ipc_alloc(self.FLAG_BYTES, C.byref(flags)))
-        self._own = (buf, flags)
-        hb, hf = C.create_string_buffer(64), C.create_string_buffer(64)
+        buf = C.c_void_p()
+        _lib.check("djv_ipc_alloc", lib.djv_ipc_alloc(lib.djv_comm_buffer_bytes(self.world, self.slot_bytes),
+                                                      C.byref(buf)))
+        self._own = (buf,)
+        hb = C.create_string_buffer(64)
         _lib.check("djv_ipc_get_handle", lib.djv_ipc_get_handle(buf, hb))
-        _lib.check("djv_ipc_get_handle", lib.djv_ipc_get_handle(flags, hf))
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, (hb.raw, hf.raw), group=process_group)
+        dist.all_gather_object(gathered, hb.raw, group=process_group)
         self._opened = []
         bufs = (C.c_void_p * self.world)()
-        flgs = (C.c_void_p * self.world)()
-        for r, (b_raw, f_raw) in enumerate(gathered):
+        for r, b_raw in enumerate(gathered):
             if r == self.rank:
-                bufs[r], flgs[r] = buf, flags
+                bufs[r] = buf
                 continue
-            pb, pf = C.c_void_p(), C.c_void_p()
+            pb = C.c_void_p()
             _lib.check("djv_ipc_open", lib.djv_ipc_open(b_raw, C.byref(pb)))
-            _lib.check("djv_ipc_open", lib.djv_ipc_open(f_raw, C.byref(pf)))
-            self._opened += [pb, pf]
-            bufs[r], flgs[r] = pb, pf
+            self._opened.append(pb)
+            bufs[r] = pb
         self._comm = C.c_void_p()
-        _lib.check("djv_comm_create", lib.djv_comm_create(C.byref(self._comm), self.rank, self.world, bufs, flgs,
-                                                          self.slot_bytes, self.SLOTS))
-        dist.barrier(group=process_group)  # every rank has mapped every buffer before the first call
+        _lib.check("djv_comm_create", lib.djv_comm_create(C.byref(self._comm), self.rank, self.world, bufs,
+                                                          self.slot_bytes))
+        # every rank has mapped every buffer and initialised its own before the first call
+        dist.barrier(group=process_group)
 
     def allreduce_add_layernorm(self, partial, residual, weight, bias, eps):
         """r = sum over ranks(partial) + residual; y = LayerNorm(r). partial, residual (B, d) fp16.

@@ -139,7 +139,6 @@ struct QkvArgs {
   int *state;
   __half *q_out, *k_cache, *v_cache;
   int S;
-  int mma_min_rows;  // (head, q|k|v) pairs with at least this many token rows go through the tensor cores
 };
 
 // ROWS weight rows against NB token rows: every activation chunk is loaded (through L1) once and used for
@@ -180,56 +179,56 @@ __device__ __forceinline__ void multi_rowdot(const uint4 *const (&wp)[ROWS], con
     for (int r = 0; r < NB; ++r) acc[j][r] = warp_sum(acc[j][r]);
 }
 
-// Tensor-core path of one block's RPB weight rows against 3..16 token rows (back-fill of K and V).
-// With that many token rows the CUDA-core path issues 8 FMAs per token row per 16-byte weight chunk and stops
+// Tensor-core path of one block's RPB weight rows against 1..16 token rows (current token + back-fill of K, V).
+// With several token rows the CUDA-core path issues 8 FMAs per token row per 16-byte weight chunk and stops
 // hiding behind the HBM stream; here the rows form m16n8k16 tiles: a tile is 16 weight rows (8 when RPB == 8,
 // the upper half of the fragment stays zero), TILES tiles per block, the block's warps split the reduction
 // dimension KW ways per tile. Lane (g, t) loads 16 contiguous bytes of weight rows g and g+8 and of token
 // rows g and g+8; the k-permutation this implies is the same on both operands, so the dot products are unchanged.
-template <int MODE, int RPB>
+// NT = 1: up to 8 token rows, NT = 2: up to 16.
+template <int MODE, int RPB, int NT>
 __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, int jrow0, int nrows,
                                              const int *rows_s, int base, float *red) {
   constexpr int TILES = (RPB == 32) ? 2 : 1;
   constexpr int KW = QKV_WARPS / TILES;
   constexpr bool HALF = (RPB == 8);
   constexpr int VALID = HALF ? 8 : 16;
-  constexpr int U = 4;
+  constexpr int U = (HALF && NT == 1) ? 8 : 4;  // weight loads in flight per lane: 8 (4 when HALF and NT == 2)
   const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
   const int g = lane / 4, t = lane % 4;
   const int tile = warp / KW, kw = warp % KW;
   const size_t wrow = ((size_t)qkv * a.nheads + h) * a.hd + jrow0 + tile * 16 + g;
   const __half *w_lo = a.w + wrow * a.d;
   const __half *w_hi = w_lo + (size_t)8 * a.d;
-  const __half *x_lo = (g < nrows) ? a.x + (size_t)rows_s[g] * a.d : nullptr;
-  const __half *x_hi = (g + 8 < nrows) ? a.x + (size_t)rows_s[g + 8] * a.d : nullptr;
-  const bool two = nrows > 8;  // block-uniform
-
-  float acc[2][4];
+  const __half *xr[NT];
 #pragma unroll
-  for (int j = 0; j < 2; ++j)
+  for (int j = 0; j < NT; ++j) xr[j] = (j * 8 + g < nrows) ? a.x + (size_t)rows_s[j * 8 + g] * a.d : nullptr;
+
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
 
   const int kblocks = (a.d + 31) / 32;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   for (int kb0 = kw; kb0 < kblocks; kb0 += KW * U) {
-    uint4 a_lo[U], a_hi[U], b_lo[U], b_hi[U];
+    uint4 a_lo[U], a_hi[U], bx[U][NT];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (kb0 + u * KW) * 32 + t * 8;
       const bool ok = k < a.d;  // d % 8 == 0: a 16-byte piece is inside the row or entirely outside
       a_lo[u] = ok ? ld_stream16(w_lo + k) : zero;
       a_hi[u] = (ok && !HALF) ? ld_stream16(w_hi + k) : zero;
-      b_lo[u] = (ok && x_lo) ? ld_cached16(x_lo + k) : zero;
-      b_hi[u] = (ok && x_hi) ? ld_cached16(x_hi + k) : zero;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) bx[u][j] = (ok && xr[j]) ? ld_cached16(xr[j] + k) : zero;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      mma_m16n8k16(acc[0], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b_lo[u].x, b_lo[u].y);
-      mma_m16n8k16(acc[0], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b_lo[u].z, b_lo[u].w);
-      if (two) {
-        mma_m16n8k16(acc[1], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b_hi[u].x, b_hi[u].y);
-        mma_m16n8k16(acc[1], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b_hi[u].z, b_hi[u].w);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        mma_m16n8k16(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, bx[u][j].x, bx[u][j].y);
+        mma_m16n8k16(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, bx[u][j].z, bx[u][j].w);
       }
     }
   }
@@ -237,15 +236,15 @@ __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, i
   // red[warp][j][row][token]
   float(*r4)[2][16][8] = reinterpret_cast<float(*)[2][16][8]>(red);
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
+  for (int j = 0; j < NT; ++j) {
     r4[warp][j][g][2 * t] = acc[j][0];
     r4[warp][j][g][2 * t + 1] = acc[j][1];
     r4[warp][j][g + 8][2 * t] = acc[j][2];
     r4[warp][j][g + 8][2 * t + 1] = acc[j][3];
   }
   __syncthreads();
-  for (int o = tid; o < TILES * 2 * 16 * 8; o += QKV_THREADS) {
-    const int c = o % 8, row = (o / 8) % 16, j = (o / 128) % 2, tl = o / 256;
+  for (int o = tid; o < TILES * NT * 16 * 8; o += QKV_THREADS) {
+    const int c = o % 8, row = (o / 8) % 16, j = (o / 128) % NT, tl = o / (128 * NT);
     const int tok = j * 8 + c;
     if (row >= VALID || tok >= nrows) continue;
     float sum = 0.f;
@@ -264,11 +263,10 @@ __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, i
       const int pos = base + trow;
       a.v_cache[((size_t)h * a.S + pos) * a.hd + jj] = out;
     } else {
-      a.q_out[(size_t)h * a.hd + jj] = out;  // MODE 1 computes q for one token row only; not reached
+      a.q_out[(size_t)h * a.hd + jj] = out;
     }
   }
 }
-
 
 // A block owns RPB = (8 / WPR) * ROWS consecutive output rows j of one (head, q|k|v) pair: each group of WPR
 // warps takes ROWS of them. Every group sees the same token rows, so the block-wide barriers are uniform.
@@ -320,12 +318,12 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
   __syncthreads();
   const int nrows = nrows_s;
   if (nrows == 0) return;
-  if constexpr (RPB == 32 || RPB == 8) {
-    if (nrows >= a.mma_min_rows) {
-      __shared__ float red_mma[QKV_WARPS * 2 * 16 * 8];
-      qkv_mma_rows<MODE, RPB>(a, qkv, h, jb * RPB, nrows, rows_s, base, red_mma);
-      return;
-    }
+  if constexpr (RPB >= 8) {
+    // full or half tensor-core tiles; measured faster than the CUDA-core path below even for one token row
+    __shared__ float red_mma[QKV_WARPS * 2 * 16 * 8];
+    if (nrows <= 8) qkv_mma_rows<MODE, RPB, 1>(a, qkv, h, jb * RPB, nrows, rows_s, base, red_mma);
+    else qkv_mma_rows<MODE, RPB, 2>(a, qkv, h, jb * RPB, nrows, rows_s, base, red_mma);
+    return;
   }
 
   const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
@@ -723,27 +721,24 @@ static int pick_wpr(long long rows, int nchunks) {
   return wpr;
 }
 
-// `rows` = output rows expected in a typical call (heads in use x 3 x head_dim). Many rows: one warp per 4
-// weight rows (32 rows per block); fewer rows: more warps per row, down to the whole block on one row.
+// `rows` = output rows expected in a typical call (heads in use x 3 x head_dim). Blocks of 32, 16 or 8 weight
+// rows run on the tensor cores with the block's 8 warps splitting the reduction dimension; the block size is
+// the largest that still gives every multiprocessor about two blocks. Very small calls put a whole block on
+// one row.
 template <int MODE>
 static void launch_qkv(QkvArgs a, int capacity_heads, long long rows, cudaStream_t st) {
   const long long sms = sm_count();
-  // development knobs, read at every launch: DJV_QKV_RPB (32, 8, 2 or 1: force the rows-per-block variant)
-  // and DJV_QKV_MMA_MIN (token rows from which a pair takes the tensor-core path; 17 switches it off)
+  // development knob, read at every launch: DJV_QKV_RPB (32, 16, 8 or 1: force the rows-per-block variant)
   const int force = env_int("DJV_QKV_RPB", 0);
-  if (force == 32 && a.hd % 32 == 0) rows = 32 * sms;
-  else if (force == 8) rows = 16 * sms;
-  else if (force == 2) rows = 8 * sms;
-  else if (force == 1) rows = 0;
-  // full 16-row tiles stream faster than the CUDA-core path even for a single token row (measured);
-  // the half-filled tiles of the 8-rows-per-block variant only pay from three token rows on
-  a.mma_min_rows = env_int("DJV_QKV_MMA_MIN", rows >= 32 * sms ? 1 : 3);
+  int rpb = (rows >= 32 * sms) ? 32 : (rows >= 16 * sms) ? 16 : (rows >= 2 * sms) ? 8 : 1;
+  if (force == 32 || force == 16 || force == 8 || force == 1) rpb = force;
+  if (a.hd % rpb != 0) rpb = 8;
 #define DJV_QKV(WPR_, ROWS_)                                                                       \
   djv::launch_kernel(qkv_sparse_kernel<MODE, WPR_, ROWS_>,                                         \
                      capacity_heads * 3 * (a.hd / ((QKV_WARPS / WPR_) * ROWS_)), QKV_THREADS, 0, st, a)
-  if (rows >= 32 * sms) DJV_QKV(1, 4);
-  else if (rows >= 16 * sms) DJV_QKV(2, 2);
-  else if (rows >= 8 * sms) DJV_QKV(4, 1);
+  if (rpb == 32) DJV_QKV(1, 4);
+  else if (rpb == 16) DJV_QKV(2, 4);
+  else if (rpb == 8) DJV_QKV(2, 2);
   else DJV_QKV(8, 1);
 #undef DJV_QKV
 }

@@ -1,25 +1,28 @@
 // Tensor-parallel one-shot all-reduce fused with the residual add and LayerNorm that follow it.
 //
-// Each rank owns an exchange buffer (2 slots) and a flag array, both mapped into every peer with CUDA
-// IPC. One call = one block per rank:
-//   1. copy this rank's fp16 partial into its own slot (epoch % 2),
-//   2. release-store epoch+1 into flag[rank] of every peer (plain stores over NVLink),
-//   3. wait (bounded) until every peer's flag in local memory reached epoch+1,
-//   4. load every rank's slot with plain peer loads, add in rank order in fp32 (same order on all
-//      ranks, so all ranks hold bit-identical results), round to fp16, add the residual, LayerNorm.
-// The epoch lives in device memory and is advanced by the kernel, so a captured CUDA graph replays
-// correctly. Two slots suffice: a rank can only reach epoch e+2 after every peer signalled e+1, which
-// a peer does after it finished reading slot e%2.
+// Push protocol, the data is its own arrival flag: every rank owns a receive buffer of
+// 3 slots x world pieces, mapped into every peer with CUDA IPC and filled with a sentinel (fp16 -0.0,
+// bits 0x8000). One call = one block per rank, step e uses slot e % 3:
+//   1. each thread stores its 16-byte chunks of this rank's partial into piece [rank] of slot e%3 of EVERY
+//      rank (plain stores over NVLink; -0.0 in the data is sent as +0.0, which changes no sum);
+//   2. each thread refills slot (e+2)%3 of the LOCAL buffer with the sentinel. That slot held step e-1,
+//      which this rank finished reading before it started step e, and no peer writes it again before step
+//      e+2, which a peer can only reach after this rank's step e+1 push, i.e. after this kernel ended;
+//   3. each thread polls (bounded) the same chunks of all pieces of the LOCAL slot e%3 until no half of a
+//      chunk is the sentinel, adds them in rank order in fp32 (same order on all ranks, so all ranks hold
+//      bit-identical results), rounds to fp16, adds the residual, and the block normalises.
+// One NVLink one-way trip per step, no fences, no remote loads. A 16-byte store may arrive in pieces: every
+// half of a chunk is checked, so a partly arrived chunk just keeps the thread polling.
+// The epoch lives in device memory and is advanced by the kernel, so a captured CUDA graph replays correctly.
 // No multicast / multimem objects are used: a peer that exits between steps cannot fault the others,
 // their next call just runs out its wait and reports DJV_ERR_TIMEOUT in the status word.
 #include "norm.cuh"
 
 struct djv_comm {
-  int rank, world, slots;
+  int rank, world;
   size_t slot_bytes;
   // device-side tables (cudaMalloc'ed by djv_comm_create)
   void **bufs_dev;
-  unsigned **flags_dev;
   unsigned *epoch_dev;  // [0] epoch, [1] status
   cudaStream_t last_stream;
 };
@@ -27,6 +30,8 @@ struct djv_comm {
 namespace djv {
 
 constexpr int AR_MAX_WORLD = 8;
+constexpr int AR_SLOTS = 3;
+constexpr unsigned AR_SENTINEL2 = 0x80008000u;  // two fp16 -0.0
 constexpr unsigned long long AR_WAIT_LIMIT_NS = 2000ull * 1000 * 1000;  // a wait on a peer gives up after 2 s
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -35,15 +40,11 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
-__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_sys16(void *p, const uint4 &v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_peer16(const void *p) {
+__device__ __forceinline__ uint4 ld_sys16(const void *p) {
   uint4 v;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
@@ -51,11 +52,28 @@ __device__ __forceinline__ uint4 ld_peer16(const void *p) {
                : "memory");
   return v;
 }
+// -0.0 halves become +0.0
+__device__ __forceinline__ unsigned no_sentinel2(unsigned w) {
+  if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;
+  if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
+  return w;
+}
+__device__ __forceinline__ bool has_sentinel2(unsigned w) {
+  return (w & 0xffffu) == 0x8000u || (w >> 16) == 0x8000u;
+}
+__device__ __forceinline__ bool arrived16(const uint4 &v) {
+  return !(has_sentinel2(v.x) || has_sentinel2(v.y) || has_sentinel2(v.z) || has_sentinel2(v.w));
+}
+
+__global__ void fill_sentinel_kernel(uint4 *p, size_t n16) {
+  const uint4 s = make_uint4(AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+    p[i] = s;
+}
 
 __global__ void __launch_bounds__(LN_THREADS)
-allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *const *__restrict__ flags,
-                               unsigned *__restrict__ epoch_status, int rank, int world,
-                               size_t slot_bytes, __half *__restrict__ y, __half *r_out,
+allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restrict__ epoch_status, int rank,
+                               int world, size_t slot_bytes, __half *__restrict__ y, __half *r_out,
                                const __half *__restrict__ partial, const __half *residual,
                                const __half *__restrict__ gamma, const __half *__restrict__ beta,
                                int B, int d, float eps) {
@@ -64,101 +82,100 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *const *
   __shared__ int failed;
   const int tid = threadIdx.x;
   const unsigned epoch = epoch_status[0];
-  const unsigned want = epoch + 1;
-  const size_t slot_off = (size_t)(epoch & 1u) * slot_bytes;
   const int nchunks = d / 8;
   const int total_chunks = B * nchunks;
   if (tid == 0) failed = 0;
   // once a wait has run out the exchange is dead: later calls return at once instead of waiting again
   if (epoch_status[1] != 0u) return;
+  __syncthreads();
+  const size_t cur_off = (size_t)(epoch % AR_SLOTS) * world * slot_bytes;
+  const size_t old_off = (size_t)((epoch + 2) % AR_SLOTS) * world * slot_bytes;
 
-  // 1. publish this rank's partial
+  // 1. push this rank's partial into piece [rank] of the current slot of every rank
   {
-    uint4 *mine = reinterpret_cast<uint4 *>(static_cast<char *>(bufs[rank]) + slot_off);
+    void *dst[AR_MAX_WORLD];
+#pragma unroll
+    for (int p = 0; p < AR_MAX_WORLD; ++p)
+      dst[p] = (p < world) ? static_cast<char *>(bufs[p]) + cur_off + (size_t)rank * slot_bytes : nullptr;
     const uint4 *src = reinterpret_cast<const uint4 *>(partial);
-    for (int c = tid; c < total_chunks; c += LN_THREADS) mine[c] = src[c];
-  }
-  __syncthreads();
-  // 2. signal every peer, 3. wait for every peer
-  if (tid < world && tid != rank) {
-    __threadfence_system();
-    st_release_sys(flags[tid] + rank, want);
-    const unsigned *f = flags[rank] + tid;
-    const unsigned long long t_start = global_timer_ns();
-    // flags only grow; a later epoch from a faster peer also satisfies the wait
-    while ((int)(ld_acquire_sys(f) - want) < 0) {
-      if (global_timer_ns() - t_start > AR_WAIT_LIMIT_NS) {
-        failed = 1;
-        break;
-      }
-      __nanosleep(100);
+    for (int c = tid; c < total_chunks; c += LN_THREADS) {
+      uint4 v = src[c];
+      v.x = no_sentinel2(v.x); v.y = no_sentinel2(v.y); v.z = no_sentinel2(v.z); v.w = no_sentinel2(v.w);
+#pragma unroll
+      for (int p = 0; p < AR_MAX_WORLD; ++p)
+        if (p < world) st_sys16(static_cast<uint4 *>(dst[p]) + c, v);
     }
-    __threadfence_system();
   }
-  __syncthreads();
-  if (failed) {
-    if (tid == 0) {
-      epoch_status[1] = (unsigned)DJV_ERR_TIMEOUT;
-      epoch_status[0] = want;
+  // 2. the slot of the previous step becomes free again
+  char *local = static_cast<char *>(bufs[rank]);
+  {
+    const uint4 s = make_uint4(AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2);
+    for (int p = 0; p < world; ++p) {
+      uint4 *old_piece = reinterpret_cast<uint4 *>(local + old_off + (size_t)p * slot_bytes);
+      for (int c = tid; c < total_chunks; c += LN_THREADS) old_piece[c] = s;
     }
-    return;
   }
 
-  // 4. reduce in rank order, residual add, LayerNorm
+  // 3. wait for the same chunks of every piece, reduce in rank order, residual add, LayerNorm
+  const unsigned long long t_start = global_timer_ns();
+  bool gave_up = false;
   for (int row = 0; row < B; ++row) {
     const size_t off = (size_t)row * d;
     float vals[LN_MAX_CHUNKS][8];
-    // All peers' pieces of two chunks are requested before the first one is used: one NVLink round trip per
-    // pair of chunks instead of one per peer.
-    constexpr int G = 2;
 #pragma unroll
-    for (int c0 = 0; c0 < LN_MAX_CHUNKS; c0 += G) {
-      uint4 v[G][AR_MAX_WORLD];
+    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+      const int ch = c * LN_THREADS + tid;
+      if (ch < nchunks && !gave_up) {
+        const char *piece0 = local + cur_off + (off + (size_t)ch * 8) * 2;
+        uint4 v[AR_MAX_WORLD];
+        unsigned missing = (1u << world) - 1u;
+        // all pieces are requested together; only the ones not there yet are asked for again
+        while (missing != 0u) {
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const int ch = (c0 + g) * LN_THREADS + tid;
+          for (int p = 0; p < AR_MAX_WORLD; ++p)
+            if (missing >> p & 1u) v[p] = ld_sys16(piece0 + (size_t)p * slot_bytes);
 #pragma unroll
-        for (int p = 0; p < AR_MAX_WORLD; ++p) {
-          if (ch < nchunks && p < world) {
-            const char *src = static_cast<const char *>(bufs[p]) + slot_off + (off + (size_t)ch * 8) * 2;
-            v[g][p] = ld_peer16(src);
-          } else {
-            v[g][p] = make_uint4(0, 0, 0, 0);
+          for (int p = 0; p < AR_MAX_WORLD; ++p)
+            if ((missing >> p & 1u) && arrived16(v[p])) missing &= ~(1u << p);
+          if (missing != 0u && global_timer_ns() - t_start > AR_WAIT_LIMIT_NS) {
+            gave_up = true;
+            break;
           }
         }
-      }
+        float f[8], t[8];
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const int c = c0 + g;
-        const int ch = c * LN_THREADS + tid;
-        if (ch < nchunks) {
-          float f[8], t[8];
+        for (int e = 0; e < 8; ++e) f[e] = 0.f;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = 0.f;
-#pragma unroll
-          for (int p = 0; p < AR_MAX_WORLD; ++p) {  // rank order; absent ranks hold zeros
-            unpack8(v[g][p], t);
+        for (int p = 0; p < AR_MAX_WORLD; ++p) {  // rank order
+          if (p < world && !gave_up) {
+            unpack8(v[p], t);
 #pragma unroll
             for (int e = 0; e < 8; ++e) f[e] += t[e];
           }
-          round_store8(f, nullptr);  // the all-reduced activation is an fp16 tensor
-          if (residual) {
-            unpack8(*reinterpret_cast<const uint4 *>(residual + off + (size_t)ch * 8), t);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] += t[e];
-          }
-          round_store8(f, r_out ? r_out + off + (size_t)ch * 8 : nullptr);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) vals[c][e] = f[e];
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) vals[c][e] = 0.f;
         }
+        round_store8(f, nullptr);  // the all-reduced activation is an fp16 tensor
+        if (residual) {
+          unpack8(*reinterpret_cast<const uint4 *>(residual + off + (size_t)ch * 8), t);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] += t[e];
+        }
+        if (!gave_up) round_store8(f, r_out ? r_out + off + (size_t)ch * 8 : nullptr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vals[c][e] = f[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vals[c][e] = 0.f;
       }
     }
+    if (gave_up) failed = 1;
+    __syncthreads();
+    if (failed) break;  // block-uniform
     layernorm_store(vals, nchunks, d, gamma, beta, eps, y + off, red);
   }
-  if (tid == 0) epoch_status[0] = want;
+  if (tid == 0) {
+    if (failed) epoch_status[1] = (unsigned)DJV_ERR_TIMEOUT;
+    epoch_status[0] = epoch + 1;
+  }
 }
 
 }  // namespace djv
@@ -223,25 +240,33 @@ extern "C" int djv_ipc_close(void *dev_ptr) {
   return DJV_OK;
 }
 
-// Set-up call: allocates three small device tables with cudaMalloc (the only allocating entry point).
-extern "C" int djv_comm_create(djv_comm **out, int rank, int world, void *const *bufs,
-                               void *const *flags, size_t slot_bytes, int slots) {
-  DJV_REQUIRE(out && bufs && flags, "comm_create: null pointer");
+extern "C" size_t djv_comm_buffer_bytes(int world, size_t slot_bytes) {
+  if (world < 1 || world > AR_MAX_WORLD) return 0;
+  return (size_t)AR_SLOTS * world * slot_bytes;
+}
+
+// Set-up call: allocates two small device tables with cudaMalloc, fills this rank's own receive buffer with
+// the sentinel and synchronises the device. Peers must not run a step before every rank has returned from
+// this call (the host puts a barrier after it).
+extern "C" int djv_comm_create(djv_comm **out, int rank, int world, void *const *bufs, size_t slot_bytes) {
+  DJV_REQUIRE(out && bufs, "comm_create: null pointer");
   DJV_REQUIRE(world >= 1 && world <= AR_MAX_WORLD && rank >= 0 && rank < world,
               "comm_create: rank %d / world %d (max %d)", rank, world, AR_MAX_WORLD);
-  DJV_REQUIRE(slots == 2, "comm_create: exactly 2 slots are used");
   DJV_REQUIRE(slot_bytes >= 16 && slot_bytes % 256 == 0, "comm_create: slot_bytes must be a multiple of 256");
   for (int r = 0; r < world; ++r)
-    DJV_REQUIRE(bufs[r] && flags[r] && aligned16(bufs[r]), "comm_create: rank %d buffer/flags missing", r);
+    DJV_REQUIRE(bufs[r] && aligned16(bufs[r]), "comm_create: rank %d buffer missing", r);
   djv_comm *c = new djv_comm();
-  c->rank = rank; c->world = world; c->slots = slots; c->slot_bytes = slot_bytes;
+  c->rank = rank; c->world = world; c->slot_bytes = slot_bytes;
   c->last_stream = nullptr;
   cudaError_t e = cudaMalloc(&c->bufs_dev, sizeof(void *) * AR_MAX_WORLD);
-  if (e == cudaSuccess) e = cudaMalloc(&c->flags_dev, sizeof(void *) * AR_MAX_WORLD);
   if (e == cudaSuccess) e = cudaMalloc(&c->epoch_dev, 2 * sizeof(unsigned));
   if (e == cudaSuccess) e = cudaMemcpy(c->bufs_dev, bufs, sizeof(void *) * world, cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = cudaMemcpy(c->flags_dev, flags, sizeof(void *) * world, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemset(c->epoch_dev, 0, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) {
+    fill_sentinel_kernel<<<64, 256>>>(static_cast<uint4 *>(bufs[rank]), djv_comm_buffer_bytes(world, slot_bytes) / 16);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     set_error("comm_create: %s", cudaGetErrorString(e));
     djv_comm_destroy(c);
@@ -254,7 +279,6 @@ extern "C" int djv_comm_create(djv_comm **out, int rank, int world, void *const 
 extern "C" int djv_comm_destroy(djv_comm *c) {
   if (!c) return DJV_OK;
   if (c->bufs_dev) cudaFree(c->bufs_dev);
-  if (c->flags_dev) cudaFree(c->flags_dev);
   if (c->epoch_dev) cudaFree(c->epoch_dev);
   delete c;
   return DJV_OK;
@@ -286,7 +310,8 @@ extern "C" int djv_allreduce_add_layernorm(djv_comm *c, void *y, void *r_out, co
               "allreduce_add_layernorm: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   c->last_stream = st;
-  djv::launch_kernel(allreduce_add_layernorm_kernel, 1, LN_THREADS, 0, st, c->bufs_dev, c->flags_dev, c->epoch_dev, c->rank, c->world, c->slot_bytes, static_cast<__half *>(y),
+  djv::launch_kernel(allreduce_add_layernorm_kernel, 1, LN_THREADS, 0, st, c->bufs_dev, c->epoch_dev, c->rank,
+                     c->world, c->slot_bytes, static_cast<__half *>(y),
       static_cast<__half *>(r_out), static_cast<const __half *>(partial),
       static_cast<const __half *>(residual), static_cast<const __half *>(gamma),
       static_cast<const __half *>(beta), B, d, eps);

@@ -230,13 +230,15 @@ int djv_add_layernorm(void *y, void *r_out, const void *x, const void *residual,
  *   r = sum_ranks(partial) + residual;  y = LN(r)
  * Replaces all_reduce(out, process_group) at mha_dejavu.py:1498 and
  * Dejavu/src/ops/fused_dense_sparse_dejavu.py:937-940 together with the add + norm of
- * block_dejavu.py:575-584, 625-636. Every rank sums the peers' partials in rank order (deterministic,
- * identical on all ranks) with plain loads over NVLink; waits on peers are bounded and report
+ * block_dejavu.py:575-584, 625-636. Every rank stores its partial into every rank's receive buffer
+ * (plain stores over NVLink, the data is its own arrival flag) and sums the pieces it received in rank
+ * order (deterministic, identical on all ranks); waits on peers are bounded and report
  * DJV_ERR_TIMEOUT through comm->status instead of hanging.
  *
  * djv_comm is created per process from peer-mapped buffers the host exchanged (CUDA IPC):
- *   bufs[r]  : rank r's exchange buffer, `slots` slots of slot_bytes each, mapped into this process
- *   flags[r] : rank r's flag array (world*slots uint32), mapped into this process
+ *   bufs[r] : rank r's receive buffer of djv_comm_buffer_bytes(world, slot_bytes) bytes, mapped into this
+ *             process; bufs[rank] is this rank's own and is initialised by djv_comm_create.
+ * Every rank must have returned from djv_comm_create before any rank runs djv_allreduce_add_layernorm.
  * ------------------------------------------------------------------------------------------- */
 typedef struct djv_comm djv_comm;
 /* Set-up helpers (these DO allocate / free with cudaMalloc / cudaFree and zero the memory): a buffer
@@ -246,8 +248,8 @@ int djv_ipc_free(void *dev_ptr);
 int djv_ipc_get_handle(const void *dev_ptr, unsigned char handle_out[64]);
 int djv_ipc_open(const unsigned char handle[64], void **dev_ptr_out);
 int djv_ipc_close(void *dev_ptr);
-int djv_comm_create(djv_comm **out, int rank, int world, void *const *bufs, void *const *flags,
-                    size_t slot_bytes, int slots);
+size_t djv_comm_buffer_bytes(int world, size_t slot_bytes);
+int djv_comm_create(djv_comm **out, int rank, int world, void *const *bufs, size_t slot_bytes);
 int djv_comm_destroy(djv_comm *comm);
 /* Reads the device status word (synchronises the stream the comm last ran on). */
 int djv_comm_status(djv_comm *comm);

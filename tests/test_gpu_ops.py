@@ -269,7 +269,7 @@ def test_topk_special_values(cuda):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("nheads,hd,d,T_,nnz", [(12, 128, 12288, 16, 4), (9, 128, 9216, 1, 3), (32, 128, 4096, 5, 12),
                                                  (8, 64, 512, 16, 8), (4, 32, 256, 3, 1)])
-@pytest.mark.parametrize("rpb", [0, 32, 8, 2])  # 0: the library's own choice; 32 and 8 have the tensor-core path
+@pytest.mark.parametrize("rpb", [0, 32, 16, 8, 1])  # 0: the library's own choice; 32, 16, 8 run on tensor cores
 def test_qkv_proj_sparse_vs_oracle(cuda, monkeypatch, nheads, hd, d, T_, nnz, rpb):
     from dejavu_b200 import ops
 
@@ -342,7 +342,7 @@ def test_add_layernorm_vs_oracle(cuda, B, d):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("nheads,hd,d,P,steps,nsel", [(6, 32, 256, 5, 37, 2), (12, 128, 1536, 40, 35, 4),
                                                        (9, 128, 1152, 130, 20, 3)])
-@pytest.mark.parametrize("rpb", [0, 32, 8])  # rows per block of the QKV kernel; 32 and 8 back-fill on tensor cores
+@pytest.mark.parametrize("rpb", [0, 32, 16, 8, 1])  # rows per block of the QKV kernel; 32, 16, 8: tensor cores
 def test_attn_step_state_machine_vs_oracle(cuda, monkeypatch, nheads, hd, d, P, steps, nsel, rpb):
     from dejavu_b200 import _lib
 
@@ -399,3 +399,95 @@ def test_attn_step_state_machine_vs_oracle(cuda, monkeypatch, nheads, hd, d, P, 
     # caches agree wherever the host model has written K,V
     close(k_dev, k_ref, atol=2e-3)
     close(v_dev, v_ref, atol=2e-3)
+
+
+# ---------------------------------------------------------------------------------------------
+# tensor-parallel exchange on one GPU: the peers' pieces are written by the test before the launch
+# (no kernel ever waits for another kernel), then a wait that nothing satisfies runs out
+# ---------------------------------------------------------------------------------------------
+def _make_comm(lib, cuda, world, slot_bytes):
+    import ctypes as C
+
+    nbytes = lib.djv_comm_buffer_bytes(world, slot_bytes)
+    assert nbytes == 3 * world * slot_bytes
+    bufs_t = [torch.zeros(nbytes // 2, dtype=torch.int16, device=cuda) for _ in range(world)]
+    bufs = (C.c_void_p * world)(*[t.data_ptr() for t in bufs_t])
+    comm = C.c_void_p()
+    from dejavu_b200 import _lib
+
+    _lib.check("djv_comm_create", lib.djv_comm_create(C.byref(comm), 0, world, bufs, slot_bytes))
+    return comm, bufs_t
+
+
+@pytest.mark.parametrize("world,B,d", [(2, 1, 9216), (4, 2, 1024), (8, 1, 12288)])
+def test_allreduce_push_protocol_single_gpu(cuda, world, B, d):
+    from dejavu_b200 import _lib
+
+    lib = _lib.load()
+    slot_bytes = (B * d * 2 + 255) // 256 * 256
+    comm, bufs_t = _make_comm(lib, cuda, world, slot_bytes)
+    SENT = -32768  # 0x8000 as int16: fp16 -0.0
+    own = bufs_t[0].view(3, world, slot_bytes // 2)
+    assert bool((own == SENT).all()), "comm_create fills the rank's own buffer with the sentinel"
+    gen = torch.Generator().manual_seed(world * d)
+    gamma, beta = (1 + rand(gen, (d,), 0.1)).to(cuda), rand(gen, (d,), 0.1).to(cuda)
+    st = torch.cuda.current_stream().cuda_stream
+    for step in range(5):
+        parts = rand(gen, (world, B, d))
+        parts[:, :, :3] = -0.0  # the sentinel value inside real data
+        res = rand(gen, (B, d))
+        slot = step % 3
+        for p in range(1, world):  # what rank p's kernel would have stored here (it sends -0.0 as +0.0)
+            piece = parts[p].clone()
+            piece[piece == 0] = 0.0
+            own[slot, p, :B * d] = piece.reshape(-1).view(torch.int16).to(cuda)
+        y = torch.empty(B, d, dtype=torch.float16, device=cuda)
+        r = torch.empty(B, d, dtype=torch.float16, device=cuda)
+        part0, resd = parts[0].to(cuda), res.to(cuda)
+        _lib.call("djv_allreduce_add_layernorm", comm, y.data_ptr(), r.data_ptr(), part0.data_ptr(), resd.data_ptr(),
+                  gamma.data_ptr(), beta.data_ptr(), B, d, 1e-5, st)
+        assert lib.djv_comm_status(comm) == 0
+        acc = torch.zeros(B, d)
+        for p in range(world):  # rank order, fp32, rounded once
+            acc += parts[p].float()
+        total = acc.half()
+        y_ref, r_ref = O.add_layernorm(total, res, gamma.cpu(), beta.cpu(), 1e-5)
+        assert torch.equal(r.cpu(), r_ref), "residual stream must be bit-exact"
+        close(y, y_ref, atol=2e-3)
+        # this rank's partial went to piece 0 of the same slot of every rank, with -0.0 sent as +0.0
+        sent = parts[0].clone()
+        sent[sent == 0] = 0.0
+        for p in range(world):
+            got = bufs_t[p].view(3, world, slot_bytes // 2)[slot, 0, :B * d].cpu()
+            assert torch.equal(got, sent.reshape(-1).view(torch.int16))
+        # the slot of the step before is free again
+        assert bool((own[(step + 2) % 3, :, :B * d] == SENT).all())
+    lib.djv_comm_destroy(comm)
+
+
+def test_allreduce_wait_runs_out_and_reports(cuda):
+    """A peer that never sends: the bounded wait gives up, the status word says so, later calls return at once."""
+    import time
+
+    from dejavu_b200 import _lib
+
+    lib = _lib.load()
+    d = 1024
+    comm, bufs_t = _make_comm(lib, cuda, 2, d * 2)
+    gen = torch.Generator().manual_seed(5)
+    x, g, b = rand(gen, (1, d)).to(cuda), torch.ones(d, dtype=torch.float16, device=cuda), torch.zeros(
+        d, dtype=torch.float16, device=cuda)
+    y, r = torch.empty_like(x), torch.empty_like(x)
+    st = torch.cuda.current_stream().cuda_stream
+    args = (comm, y.data_ptr(), r.data_ptr(), x.data_ptr(), None, g.data_ptr(), b.data_ptr(), 1, d, 1e-5, st)
+    t0 = time.time()
+    _lib.call("djv_allreduce_add_layernorm", *args)
+    assert lib.djv_comm_status(comm) == _lib.ERR_TIMEOUT
+    assert 1.0 < time.time() - t0 < 20.0
+    t0 = time.time()
+    _lib.call("djv_allreduce_add_layernorm", *args)
+    assert lib.djv_comm_status(comm) == _lib.ERR_TIMEOUT
+    assert time.time() - t0 < 1.0, "a dead exchange must not wait again"
+    # the context is still usable
+    assert torch.equal((x + 1).cpu(), x.cpu() + 1)
+    lib.djv_comm_destroy(comm)
