@@ -8,10 +8,14 @@
 //   V cache (B, nheads, S, hd)        element (h, pos, j) at (h*S + pos)*hd + j
 //
 // Algorithmic bytes: QKV 3*a*hd*d*2 (+bias, x); attention 2*a*len*hd*2; out_proj d*a*hd*2 (+bias, ctx, y).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "rowdot_mma.cuh"
 
 namespace djv {
+
+namespace cg = cooperative_groups;
 
 // ------------------------------------------------------------------------------------------
 // state words, see DJV_ATTN_STATE_* in the header
@@ -422,12 +426,14 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
 
 // ------------------------------------------------------------------------------------------
 // Single-query attention for a list of heads, split over the cached tokens.
-// grid = (head slots, batch, splits); 128 threads. Partial (max, sum, out[hd]) per split goes to
-// scratch; the last split to finish for a (head, batch) combines them and writes fp16 context.
-// scratch layout: [counters: 4096 B][partials: slots*B*splits*(hd+2) floats]
+// grid = (head slots, batch, splits); 128 threads; the splits of one (head, batch) form a thread-block
+// cluster. Each split leaves its partial (max, sum, out[hd]) in its own shared memory; after a cluster
+// barrier split 0 reads them through distributed shared memory, combines and writes the fp16 context.
+// No global scratch, no atomics.
 // ------------------------------------------------------------------------------------------
 constexpr int AT_THREADS = 128;
 constexpr int AT_MAX_SPLIT_TOKENS = 512;  // tokens one block handles at most per pass
+constexpr int AT_MAX_SPLITS = 8;          // portable cluster size
 constexpr int AT_COUNTER_BYTES = 4096;
 
 struct AttnArgs {
@@ -438,8 +444,6 @@ struct AttnArgs {
   const int *state;      // when non-null: heads/n_eff/len come from the lazy-KV state
   int nnz, nheads, hd, S, len;
   float scale;
-  float *partial;
-  unsigned *counters;
 };
 
 template <int HD>
@@ -570,41 +574,40 @@ __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
     for (int r = 0; r < RPI; ++r) o += osum[r][tid];
   }
 
-  const size_t slot_id = (size_t)i * gridDim.y + b;
   if (nsplit == 1) {
     if (tid < HD) a.ctx[bh * HD + tid] = __float2half_rn(l_run > 0.f ? o / l_run : 0.f);
     return;
   }
-  float *part = a.partial + (slot_id * nsplit + sp) * (HD + 2);
-  if (tid < HD) __stcg(part + 2 + tid, o);
+  // the cluster spans the whole z extent of the grid: block rank in the cluster == sp.
+  // Every block of a cluster took the same branch at `i >= n_eff`, so the barriers are cluster-uniform.
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float part_s[HD + 2];
+  if (tid < HD) part_s[2 + tid] = o;
   if (tid == 0) {
-    __stcg(part, m_run);
-    __stcg(part + 1, l_run);
+    part_s[0] = m_run;
+    part_s[1] = l_run;
   }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned ticket = atomicAdd(&a.counters[slot_id], 1u);
-    is_last = (ticket == (unsigned)nsplit - 1);
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  if (tid < HD) {
-    const float *p0 = a.partial + slot_id * nsplit * (HD + 2);
+  cluster.sync();
+  if (sp == 0 && tid < HD) {
+    float ms[AT_MAX_SPLITS];
     float m = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, __ldcg(p0 + (size_t)s * (HD + 2)));
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+      ms[s] = (s < nsplit) ? *cluster.map_shared_rank(&part_s[0], s) : -INFINITY;
+      m = fmaxf(m, ms[s]);
+    }
     float l = 0.f, acc = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      const float ms = __ldcg(p0 + (size_t)s * (HD + 2));
-      if (ms == -INFINITY) continue;
-      const float w = __expf(ms - m);
-      l += w * __ldcg(p0 + (size_t)s * (HD + 2) + 1);
-      acc += w * __ldcg(p0 + (size_t)s * (HD + 2) + 2 + tid);
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+      if (s < nsplit && ms[s] != -INFINITY) {
+        const float w = __expf(ms[s] - m);
+        l += w * *cluster.map_shared_rank(&part_s[1], s);
+        acc += w * *cluster.map_shared_rank(&part_s[2 + tid], s);
+      }
     }
     a.ctx[bh * HD + tid] = __float2half_rn(l > 0.f ? acc / l : 0.f);
   }
-  if (tid == 0) a.counters[slot_id] = 0;
+  cluster.sync();  // no block leaves while split 0 may still read its shared memory
 }
 
 // ------------------------------------------------------------------------------------------
@@ -861,7 +864,7 @@ extern "C" int djv_attn_state_reset(int32_t *state, int nheads, int prompt_len, 
 
 static int attn_splits(int S) {
   int s = ceil_div(S, 128);
-  if (s > 16) s = 16;
+  if (s > AT_MAX_SPLITS) s = AT_MAX_SPLITS;
   if (s < 1) s = 1;
   return s;
 }
@@ -870,23 +873,16 @@ static size_t attn_scratch_bytes(int slots, int B, int hd, int S) {
   return AT_COUNTER_BYTES + (size_t)slots * B * attn_splits(S) * (hd + 2) * sizeof(float);
 }
 
+// `scratch` is not used any more (the splits combine through distributed shared memory); the parameters stay
+// in the C signatures so that existing callers keep working.
 static int launch_attn(AttnArgs a, int slots, int B, void *scratch, size_t scratch_bytes, cudaStream_t st,
                        const char *op) {
+  (void)scratch; (void)scratch_bytes; (void)op;
   const int nsplit = attn_splits(a.S);
-  const size_t need = attn_scratch_bytes(slots, B, a.hd, a.S);
-  if (nsplit > 1) {
-    if (!scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
-      set_error("%s: scratch needs %zu bytes, 256-byte aligned (got %zu)", op, need, scratch_bytes);
-      return DJV_ERR_SCRATCH;
-    }
-    DJV_REQUIRE((size_t)slots * B * sizeof(unsigned) <= AT_COUNTER_BYTES, "%s: too many (head,batch) slots", op);
-    a.counters = reinterpret_cast<unsigned *>(scratch);
-    a.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + AT_COUNTER_BYTES);
-  }
-  dim3 grid(slots, B, nsplit);
-  if (a.hd == 128) djv::launch_kernel(decode_attn_kernel<128>, grid, AT_THREADS, 0, st, a);
-  else if (a.hd == 64) djv::launch_kernel(decode_attn_kernel<64>, grid, AT_THREADS, 0, st, a);
-  else djv::launch_kernel(decode_attn_kernel<32>, grid, AT_THREADS, 0, st, a);
+  dim3 grid(slots, B, nsplit), cluster(1, 1, nsplit);
+  if (a.hd == 128) djv::launch_kernel_cluster(decode_attn_kernel<128>, grid, AT_THREADS, 0, st, cluster, a);
+  else if (a.hd == 64) djv::launch_kernel_cluster(decode_attn_kernel<64>, grid, AT_THREADS, 0, st, cluster, a);
+  else djv::launch_kernel_cluster(decode_attn_kernel<32>, grid, AT_THREADS, 0, st, cluster, a);
   count_launch();
   return DJV_OK;
 }

@@ -55,6 +55,27 @@ inline cudaError_t launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, si
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
 }
 
+// The same with thread-block clusters of `cluster` blocks (for kernels without compile-time cluster dims).
+template <typename... P, typename... A>
+inline cudaError_t launch_kernel_cluster(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                         dim3 cluster, A &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 // ---- device side --------------------------------------------------------------------------
 constexpr int WARP = 32;
 
