@@ -69,12 +69,14 @@ __device__ __forceinline__ int block_exscan(int v, int *warp_sums, int *total) {
 template <typename T>
 __global__ void __launch_bounds__(TK_THREADS)
 topk_kernel(int32_t *__restrict__ idx32, int64_t *__restrict__ idx64, const T *__restrict__ scores,
-            int n, int K) {
+            int n, int K, int n_sub) {
   pdl_prologue();
   using Key = typename KeyTraits<T>::Key;
   constexpr int BITS = KeyTraits<T>::BITS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  Key *keys = reinterpret_cast<Key *>(smem_raw);
+  // [n_sub histograms of 256 counters][n keys]
+  int *sub_hist = reinterpret_cast<int *>(smem_raw);
+  Key *keys = reinterpret_cast<Key *>(smem_raw + (size_t)n_sub * 256 * sizeof(int));
   __shared__ int hist[256];
   __shared__ int warp_sums[TK_WARPS];
   __shared__ int s_total;
@@ -82,6 +84,7 @@ topk_kernel(int32_t *__restrict__ idx32, int64_t *__restrict__ idx64, const T *_
   __shared__ int s_need;
 
   const int tid = threadIdx.x;
+  for (int i = tid; i < n_sub * 256; i += TK_THREADS) sub_hist[i] = 0;
   for (int i = tid; i < n; i += TK_THREADS) keys[i] = (Key)key_of(scores[i]);
   if (tid == 0) {
     s_prefix = 0;
@@ -91,13 +94,25 @@ topk_kernel(int32_t *__restrict__ idx32, int64_t *__restrict__ idx64, const T *_
 
   unsigned mask = 0;
   for (int shift = BITS - 8; shift >= 0; shift -= 8) {
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
     const unsigned prefix = s_prefix;
     const int need = s_need;
-    for (int i = tid; i < n; i += TK_THREADS) {
-      const unsigned k = keys[i];
-      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xffu], 1);
+    // Scores cluster in a few exponent bins, so all warps adding into one histogram would serialise on a
+    // handful of shared-memory words: every group of warps counts into its own copy, added up afterwards.
+    {
+      int *my_hist = sub_hist + (tid / WARP % n_sub) * 256;
+      for (int i = tid; i < n; i += TK_THREADS) {
+        const unsigned k = keys[i];
+        if ((k & mask) == prefix) atomicAdd(&my_hist[(k >> shift) & 0xffu], 1);
+      }
+    }
+    __syncthreads();
+    if (tid < 256) {
+      int sum = 0;
+      for (int c = 0; c < n_sub; ++c) {
+        sum += sub_hist[c * 256 + tid];
+        sub_hist[c * 256 + tid] = 0;
+      }
+      hist[tid] = sum;
     }
     __syncthreads();
     // warp 0: find the bin holding the need-th largest key among the candidates
@@ -186,16 +201,18 @@ extern "C" int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int 
   }
   if (K == 0) return DJV_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t smem = (bytes + 15) & ~(size_t)15;
+  // one histogram copy per warp while the keys leave room, else one per 4 warps
+  const int n_sub = (bytes <= 160 * 1024) ? TK_WARPS : TK_WARPS / 4;
+  const size_t smem = ((bytes + 15) & ~(size_t)15) + (size_t)n_sub * 256 * sizeof(int);
   cudaError_t e;
   if (score_is_f32) {
-    e = cudaFuncSetAttribute(topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    e = cudaFuncSetAttribute(topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     if (e == cudaSuccess)
-      djv::launch_kernel(topk_kernel<float>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const float *>(scores), n, K);
+      djv::launch_kernel(topk_kernel<float>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const float *>(scores), n, K, n_sub);
   } else {
-    e = cudaFuncSetAttribute(topk_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    e = cudaFuncSetAttribute(topk_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     if (e == cudaSuccess)
-      djv::launch_kernel(topk_kernel<__half>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const __half *>(scores), n, K);
+      djv::launch_kernel(topk_kernel<__half>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const __half *>(scores), n, K, n_sub);
   }
   if (e != cudaSuccess) {
     set_error("topk: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
