@@ -432,7 +432,6 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
 // No global scratch, no atomics.
 // ------------------------------------------------------------------------------------------
 constexpr int AT_THREADS = 128;
-constexpr int AT_MAX_SPLIT_TOKENS = 512;  // tokens one block handles at most per pass
 constexpr int AT_MAX_SPLITS = 8;          // portable cluster size
 constexpr int AT_COUNTER_BYTES = 4096;
 
@@ -452,10 +451,9 @@ __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
   constexpr int CH = HD / 8;           // 16-byte chunks per head row
   constexpr int RPI = AT_THREADS / CH; // V rows per iteration
   __shared__ float qs[HD];
-  __shared__ float sc[AT_MAX_SPLIT_TOKENS];
+  __shared__ float sc[AT_THREADS];
   __shared__ float redf[AT_THREADS / WARP];
   __shared__ float osum[RPI][HD];
-  __shared__ int is_last;
 
   const int tid = threadIdx.x, lane = tid % WARP, warp = tid / WARP;
   const int i = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
@@ -474,8 +472,6 @@ __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
   const size_t bh = (size_t)b * a.nheads + h;
   const __half *Kh = a.k_cache + bh * (size_t)a.S * HD;
   const __half *Vh = a.v_cache + bh * (size_t)a.S * HD;
-  for (int j = tid; j < HD; j += AT_THREADS) qs[j] = __half2float(a.q[bh * HD + j]) * a.scale;
-  __syncthreads();
 
   const int chunk = (len + nsplit - 1) / nsplit;
   const int t_begin = min(len, sp * chunk), t_end = min(len, t_begin + chunk);
@@ -485,18 +481,32 @@ __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
 #pragma unroll
   for (int e = 0; e < 8; ++e) oacc[e] = 0.f;
   const int vrow = tid / CH, vch = tid % CH;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
 
-  for (int p0 = t_begin; p0 < t_end; p0 += AT_MAX_SPLIT_TOKENS) {
-    const int pn = min(AT_MAX_SPLIT_TOKENS, t_end - p0);
-    // scores: one thread per token
-    float lmax = -INFINITY;
-    for (int t = tid; t < pn; t += AT_THREADS) {
-      const int pos = p0 + t;
-      float s = 0.f;
+  // A pass covers AT_THREADS tokens: thread t scores token t (CH 16-byte loads of K) and, for P.V, thread
+  // (vrow, vch) reads chunk vch of V rows vrow, vrow+RPI, ... (CH loads). All 2*CH loads of a pass, and q in the
+  // first pass, are issued before anything waits on them, so a pass costs one trip to HBM instead of three.
+  for (int p0 = t_begin; p0 < t_end; p0 += AT_THREADS) {
+    const int pn = min(AT_THREADS, t_end - p0);
+    uint4 kreg[CH], vreg[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+      kreg[c] = (tid < pn) ? ld_stream16(Kh + ((size_t)c * a.S + p0 + tid) * 8) : zero;
+#pragma unroll
+    for (int it = 0; it < CH; ++it) {
+      const int t = it * RPI + vrow;
+      vreg[it] = (t < pn) ? ld_stream16(Vh + (size_t)(p0 + t) * HD + vch * 8) : zero;
+    }
+    if (p0 == t_begin) {
+      for (int j = tid; j < HD; j += AT_THREADS) qs[j] = __half2float(a.q[bh * HD + j]) * a.scale;
+      __syncthreads();
+    }
+    float s = -INFINITY;
+    if (tid < pn) {
+      s = 0.f;
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        const uint4 kv = ld_stream16(Kh + ((size_t)c * a.S + pos) * 8);
-        const float2 k0 = h2f(kv.x), k1 = h2f(kv.y), k2 = h2f(kv.z), k3 = h2f(kv.w);
+        const float2 k0 = h2f(kreg[c].x), k1 = h2f(kreg[c].y), k2 = h2f(kreg[c].z), k3 = h2f(kreg[c].w);
         s = fmaf(qs[c * 8 + 0], k0.x, s);
         s = fmaf(qs[c * 8 + 1], k0.y, s);
         s = fmaf(qs[c * 8 + 2], k1.x, s);
@@ -506,25 +516,19 @@ __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
         s = fmaf(qs[c * 8 + 6], k3.x, s);
         s = fmaf(qs[c * 8 + 7], k3.y, s);
       }
-      sc[t] = s;
-      lmax = fmaxf(lmax, s);
     }
-    lmax = warp_max(lmax);
+    float lmax = warp_max(s);
     if (lane == 0) redf[warp] = lmax;
     __syncthreads();
     float m_new = m_run;
 #pragma unroll
     for (int w2 = 0; w2 < AT_THREADS / WARP; ++w2) m_new = fmaxf(m_new, redf[w2]);
     __syncthreads();
-    float lsum = 0.f;
-    for (int t = tid; t < pn; t += AT_THREADS) {
-      const float p = __expf(sc[t] - m_new);
-      sc[t] = p;
-      lsum += p;
-    }
-    lsum = warp_sum(lsum);
+    const float p = (tid < pn) ? __expf(s - m_new) : 0.f;
+    sc[tid] = p;
+    float lsum = warp_sum(p);
     if (lane == 0) redf[warp] = lsum;
-    __syncthreads();
+    __syncthreads();  // sc[] and redf[] complete
     float ltot = 0.f;
 #pragma unroll
     for (int w2 = 0; w2 < AT_THREADS / WARP; ++w2) ltot += redf[w2];
@@ -533,34 +537,18 @@ __global__ void __launch_bounds__(AT_THREADS) decode_attn_kernel(AttnArgs a) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) oacc[e] *= corr;
     m_run = m_new;
-    // P.V: CH lanes cover one V row, RPI rows per iteration, 4 iterations' loads in flight
-    for (int t0 = vrow; t0 < pn; t0 += RPI * 4) {
-      uint4 vv[4];
-      float pw[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int t = t0 + u * RPI;
-        if (t < pn) {
-          vv[u] = ld_stream16(Vh + (size_t)(p0 + t) * HD + vch * 8);
-          pw[u] = sc[t];
-        } else {
-          vv[u] = make_uint4(0, 0, 0, 0);
-          pw[u] = 0.f;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float p = pw[u];
-        const float2 v0 = h2f(vv[u].x), v1 = h2f(vv[u].y), v2 = h2f(vv[u].z), v3 = h2f(vv[u].w);
-        oacc[0] = fmaf(p, v0.x, oacc[0]);
-        oacc[1] = fmaf(p, v0.y, oacc[1]);
-        oacc[2] = fmaf(p, v1.x, oacc[2]);
-        oacc[3] = fmaf(p, v1.y, oacc[3]);
-        oacc[4] = fmaf(p, v2.x, oacc[4]);
-        oacc[5] = fmaf(p, v2.y, oacc[5]);
-        oacc[6] = fmaf(p, v3.x, oacc[6]);
-        oacc[7] = fmaf(p, v3.y, oacc[7]);
-      }
+    for (int it = 0; it < CH; ++it) {
+      const float pw = sc[it * RPI + vrow];  // 0 for tokens past the end of the pass
+      const float2 v0 = h2f(vreg[it].x), v1 = h2f(vreg[it].y), v2 = h2f(vreg[it].z), v3 = h2f(vreg[it].w);
+      oacc[0] = fmaf(pw, v0.x, oacc[0]);
+      oacc[1] = fmaf(pw, v0.y, oacc[1]);
+      oacc[2] = fmaf(pw, v1.x, oacc[2]);
+      oacc[3] = fmaf(pw, v1.y, oacc[3]);
+      oacc[4] = fmaf(pw, v2.x, oacc[4]);
+      oacc[5] = fmaf(pw, v2.y, oacc[5]);
+      oacc[6] = fmaf(pw, v3.x, oacc[6]);
+      oacc[7] = fmaf(pw, v3.y, oacc[7]);
     }
     __syncthreads();  // sc[] and redf[] are reused by the next pass
   }

@@ -201,8 +201,11 @@ extern "C" int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int 
   }
   if (K == 0) return DJV_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // one histogram copy per warp while the keys leave room, else one per 4 warps
-  const int n_sub = (bytes <= 160 * 1024) ? TK_WARPS : TK_WARPS / 4;
+  // Four histogram copies (one per 8 warps). One per warp was measured slower inside a decode step: this
+  // block shares its multiprocessor with blocks of the main chain, and the extra shared-memory traffic of
+  // 32 copies slowed those down enough to stretch the kernels they belong to.
+  static const int k_sub = env_int("DJV_TK_SUB", 4);  // development knob
+  const int n_sub = (k_sub >= 1 && k_sub <= TK_WARPS) ? k_sub : 4;
   const size_t smem = ((bytes + 15) & ~(size_t)15) + (size_t)n_sub * 256 * sizeof(int);
   cudaError_t e;
   if (score_is_f32) {
