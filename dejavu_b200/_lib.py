@@ -47,7 +47,8 @@ SIGNATURES = {
     "djv_attn_state_reset": (_i, [_vp, _i, _i, _vp]),
     "djv_attn_step_scratch_bytes": (_sz, [_i, _i, _i]),
     "djv_attn_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
-    "djv_attn_step_project": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "djv_attn_step_project": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "djv_topk_attn_prep": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "djv_attn_step_attend": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _sz, _vp]),
     "djv_attn_step_finish": (_i, [_vp, _i, _vp]),
     "djv_decode_attn_scratch_bytes": (_sz, [_i, _i, _i, _i]),

@@ -10,22 +10,13 @@
 // Algorithmic bytes: QKV 3*a*hd*d*2 (+bias, x); attention 2*a*len*hd*2; out_proj d*a*hd*2 (+bias, ctx, y).
 #include <cooperative_groups.h>
 
+#include "attn_state.cuh"
 #include "common.cuh"
 #include "rowdot_mma.cuh"
 
 namespace djv {
 
 namespace cg = cooperative_groups;
-
-// ------------------------------------------------------------------------------------------
-// state words, see DJV_ATTN_STATE_* in the header
-// ------------------------------------------------------------------------------------------
-enum { ST_SLOT = 0, ST_BASE = 1, ST_NEFF = 2, ST_STATUS = 3, ST_OPEN = 4 };  // ST_OPEN: a step awaits its advance
-__device__ __forceinline__ int *st_pending(int *st) { return st + DJV_ATTN_STATE_HDR; }
-__device__ __forceinline__ int *st_eff(int *st, int nheads) { return st + DJV_ATTN_STATE_HDR + nheads; }
-__device__ __forceinline__ int *st_rowmask(int *st, int nheads) {
-  return st + DJV_ATTN_STATE_HDR + 2 * nheads;
-}
 
 __global__ void attn_state_reset_kernel(int *st, int nheads, int prompt_len) {
   pdl_prologue();
@@ -35,76 +26,12 @@ __global__ void attn_state_reset_kernel(int *st, int nheads, int prompt_len) {
   if (threadIdx.x == 0) st[ST_BASE] = prompt_len;
 }
 
-// Step 1 of djv_attn_step: stash x in the window, pick the heads in use, update `pending`.
+// Step 1 of djv_attn_step as a kernel of its own (see attn_prep_block).
 __global__ void __launch_bounds__(1024)
 attn_prep_kernel(int *__restrict__ st, const int *__restrict__ head_idx, int nnz,
                  const __half *__restrict__ x, __half *__restrict__ x_ring, int d, int nheads, int S) {
   pdl_prologue();
-  const int tid = threadIdx.x;
-  int slot = st[ST_SLOT], base = st[ST_BASE];
-  // the previous step was not closed by djv_attn_step_finish: advance past it first
-  if (st[ST_OPEN] != 0 && st[ST_STATUS] == 0) {
-    if (++slot >= DJV_KV_WINDOW) {
-      slot = 0;
-      base += DJV_KV_WINDOW;
-    }
-  }
-  __syncthreads();  // every thread has read the old words
-  if (tid == 0) {
-    st[ST_SLOT] = slot;
-    st[ST_BASE] = base;
-    st[ST_OPEN] = 1;
-  }
-  int *pending = st_pending(st), *eff = st_eff(st, nheads), *rowmask = st_rowmask(st, nheads);
-  const bool bad = slot < 0 || slot >= DJV_KV_WINDOW || base < 0 || base + slot >= S;
-  if (bad) {
-    if (tid == 0) {
-      st[ST_STATUS] = DJV_ERR_INVALID;
-      st[ST_NEFF] = 0;
-    }
-    return;
-  }
-  // x_ring[slot] = x
-  const uint4 *src = reinterpret_cast<const uint4 *>(x);
-  uint4 *dst = reinterpret_cast<uint4 *>(x_ring + (size_t)slot * d);
-  for (int c = tid; c < d / 8; c += blockDim.x) dst[c] = src[c];
-
-  const bool all = (head_idx == nullptr) || (slot == DJV_KV_WINDOW - 1);
-  const int bit = 1 << slot;
-  __shared__ int selected[1024];
-  __shared__ int warp_tot[32];
-  for (int h = tid; h < nheads; h += blockDim.x) selected[h] = all ? 1 : 0;
-  __syncthreads();
-  if (!all)
-    for (int i = tid; i < nnz; i += blockDim.x) {
-      const int h = head_idx[i];
-      if (h >= 0 && h < nheads) selected[h] = 1;  // duplicates collapse here
-    }
-  __syncthreads();
-  // heads in use are emitted in ascending head order: exclusive scan of the flags (nheads <= 1024)
-  const int lane = tid % WARP, warp = tid / WARP;
-  const int flag = (tid < nheads) ? selected[tid] : 0;
-  const unsigned ballot = __ballot_sync(0xffffffffu, flag);
-  const int in_warp = __popc(ballot & ((1u << lane) - 1u));
-  if (lane == 0) warp_tot[warp] = __popc(ballot);
-  __syncthreads();
-  int before = 0, total = 0;
-  for (int w2 = 0; w2 < 32; ++w2) {
-    const int t = warp_tot[w2];
-    if (w2 < warp) before += t;
-    total += t;
-  }
-  if (tid < nheads) {
-    if (flag) {
-      const int pos = before + in_warp;
-      eff[pos] = tid;
-      rowmask[pos] = pending[tid] | bit;
-      pending[tid] = 0;
-    } else {
-      pending[tid] |= bit;
-    }
-  }
-  if (tid == 0) st[ST_NEFF] = total;
+  attn_prep_block(st, head_idx, nnz, x, x_ring, d, nheads, S);
 }
 
 __global__ void attn_finish_kernel(int *st) {
@@ -143,6 +70,10 @@ struct QkvArgs {
   int *state;
   __half *q_out, *k_cache, *v_cache;
   int S;
+  // MODE 1 when the step was opened without the stash of x (djv_topk_attn_prep): the current token row is read
+  // from x_cur, and block 0 copies it into the window for later back-fills. Null otherwise.
+  const __half *x_cur;
+  __half *x_ring_w;
 };
 
 // ROWS weight rows against NB token rows: every activation chunk is loaded (through L1) once and used for
@@ -192,7 +123,7 @@ __device__ __forceinline__ void multi_rowdot(const uint4 *const (&wp)[ROWS], con
 // NT = 1: up to 8 token rows, NT = 2: up to 16.
 template <int MODE, int RPB, int NT>
 __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, int jrow0, int nrows,
-                                             const int *rows_s, int base, float *red) {
+                                             const int *rows_s, int base, int cur_slot, float *red) {
   constexpr int TILES = (RPB == 32) ? 2 : 1;
   constexpr int KW = QKV_WARPS / TILES;
   constexpr bool HALF = (RPB == 8);
@@ -206,7 +137,13 @@ __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, i
   const __half *w_hi = w_lo + (size_t)8 * a.d;
   const __half *xr[NT];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) xr[j] = (j * 8 + g < nrows) ? a.x + (size_t)rows_s[j * 8 + g] * a.d : nullptr;
+  for (int j = 0; j < NT; ++j) {
+    xr[j] = nullptr;
+    if (j * 8 + g < nrows) {
+      const int r = rows_s[j * 8 + g];
+      xr[j] = (MODE == 1 && a.x_cur != nullptr && r == cur_slot) ? a.x_cur : a.x + (size_t)r * a.d;
+    }
+  }
 
   float acc[NT][4];
 #pragma unroll
@@ -296,6 +233,12 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
     n_eff = a.state[ST_NEFF];
     slot = a.state[ST_SLOT];
     base = a.state[ST_BASE];
+    if (a.x_cur != nullptr && blockIdx.x == 0 && a.state[ST_STATUS] == 0) {
+      // nobody reads window row `slot` in this kernel: the current token is taken from x_cur
+      const uint4 *src = reinterpret_cast<const uint4 *>(a.x_cur);
+      uint4 *dst = reinterpret_cast<uint4 *>(a.x_ring_w + (size_t)slot * a.d);
+      for (int c = threadIdx.x; c < a.d / 8; c += QKV_THREADS) dst[c] = src[c];
+    }
   }
   if (i >= n_eff) return;
   const int h = (MODE == 0) ? a.head_idx[i] : st_eff(a.state, a.nheads)[i];
@@ -325,8 +268,8 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
   if constexpr (RPB >= 8) {
     // full or half tensor-core tiles; measured faster than the CUDA-core path below even for one token row
     __shared__ float red_mma[QKV_WARPS * 2 * 16 * 8];
-    if (nrows <= 8) qkv_mma_rows<MODE, RPB, 1>(a, qkv, h, jb * RPB, nrows, rows_s, base, red_mma);
-    else qkv_mma_rows<MODE, RPB, 2>(a, qkv, h, jb * RPB, nrows, rows_s, base, red_mma);
+    if (nrows <= 8) qkv_mma_rows<MODE, RPB, 1>(a, qkv, h, jb * RPB, nrows, rows_s, base, slot, red_mma);
+    else qkv_mma_rows<MODE, RPB, 2>(a, qkv, h, jb * RPB, nrows, rows_s, base, slot, red_mma);
     return;
   }
 
@@ -351,7 +294,11 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
     float acc[ROWS][NBMAX];
     const uint4 *xp[NBMAX];
 #pragma unroll
-    for (int r = 0; r < NBMAX; ++r) xp[r] = Xv + (size_t)rows_s[r0 + (r < nb ? r : 0)] * nchunks;
+    for (int r = 0; r < NBMAX; ++r) {
+      const int tr = rows_s[r0 + (r < nb ? r : 0)];
+      xp[r] = (MODE == 1 && a.x_cur != nullptr && tr == slot) ? reinterpret_cast<const uint4 *>(a.x_cur)
+                                                              : Xv + (size_t)tr * nchunks;
+    }
     if (nb == 1) {
       const uint4 *x1[1] = {xp[0]};
       float a1[ROWS][1];
@@ -883,7 +830,7 @@ extern "C" size_t djv_attn_step_scratch_bytes(int nheads, int hd, int S) {
 extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x,
                                      void *x_ring, void *k_cache, void *v_cache, int32_t *state,
                                      const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
-                                     void *stream) {
+                                     int step_is_open, void *stream) {
   DJV_REQUIRE(q_out && wqkv && x && x_ring && k_cache && v_cache && state, "attn_step: null pointer");
   int rc = check_hd("attn_step", hd, d);
   if (rc) return rc;
@@ -893,9 +840,11 @@ extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *
   DJV_REQUIRE(aligned16(wqkv) && aligned16(x) && aligned16(x_ring) && aligned16(k_cache) && aligned16(v_cache),
               "attn_step: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  djv::launch_kernel(attn_prep_kernel, 1, 1024, 0, st, state, head_idx, head_idx ? nnz : 0, static_cast<const __half *>(x),
-                                       static_cast<__half *>(x_ring), d, nheads, S);
-  count_launch();
+  if (!step_is_open) {
+    djv::launch_kernel(attn_prep_kernel, 1, 1024, 0, st, state, head_idx, head_idx ? nnz : 0,
+                       static_cast<const __half *>(x), static_cast<__half *>(x_ring), d, nheads, S);
+    count_launch();
+  }
   QkvArgs a{};
   a.w = static_cast<const __half *>(wqkv);
   a.bias = static_cast<const __half *>(bqkv);
@@ -906,6 +855,10 @@ extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *
   a.k_cache = static_cast<__half *>(k_cache);
   a.v_cache = static_cast<__half *>(v_cache);
   a.S = S;
+  if (step_is_open) {
+    a.x_cur = static_cast<const __half *>(x);
+    a.x_ring_w = static_cast<__half *>(x_ring);
+  }
   const int typical = head_idx ? (nnz > 0 ? nnz : 1) : nheads;
   launch_qkv<1>(a, nheads, (long long)typical * 3 * hd, st);
   count_launch();
@@ -939,7 +892,7 @@ extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const voi
                              float softmax_scale, void *scratch, size_t scratch_bytes, void *stream) {
   DJV_REQUIRE(ctx != nullptr, "attn_step: null pointer");
   int rc = djv_attn_step_project(q_out, wqkv, bqkv, x, x_ring, k_cache, v_cache, state, head_idx, nnz, d, nheads,
-                                 hd, S, stream);
+                                 hd, S, 0, stream);
   if (rc) return rc;
   return djv_attn_step_attend(ctx, q_out, k_cache, v_cache, state, nheads, hd, S, softmax_scale, scratch,
                               scratch_bytes, stream);

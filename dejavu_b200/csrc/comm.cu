@@ -71,18 +71,23 @@ __global__ void fill_sentinel_kernel(uint4 *p, size_t n16) {
     p[i] = s;
 }
 
+template <int NCH>
 __global__ void __launch_bounds__(LN_THREADS)
 allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restrict__ epoch_status, int rank,
                                int world, size_t slot_bytes, __half *__restrict__ y, __half *r_out,
                                const __half *__restrict__ partial, const __half *residual,
                                const __half *__restrict__ gamma, const __half *__restrict__ beta,
                                int B, int d, float eps) {
-  pdl_prologue();
   __shared__ float red[LN_THREADS / WARP];
   __shared__ int failed;
   const int tid = threadIdx.x;
-  const unsigned epoch = epoch_status[0];
   const int nchunks = d / 8;
+  // the affine weights are fetched while the predecessor kernel may still be running
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  LnAffine<NCH> w;
+  ln_fetch_affine(w, gamma, beta, nchunks);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const unsigned epoch = epoch_status[0];
   const int total_chunks = B * nchunks;
   if (tid == 0) failed = 0;
   // once a wait has run out the exchange is dead: later calls return at once instead of waiting again
@@ -121,9 +126,9 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restr
   bool gave_up = false;
   for (int row = 0; row < B; ++row) {
     const size_t off = (size_t)row * d;
-    float vals[LN_MAX_CHUNKS][8];
+    float vals[NCH][8];
 #pragma unroll
-    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+    for (int c = 0; c < NCH; ++c) {
       const int ch = c * LN_THREADS + tid;
       if (ch < nchunks && !gave_up) {
         const char *piece0 = local + cur_off + (off + (size_t)ch * 8) * 2;
@@ -170,7 +175,7 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restr
     if (gave_up) failed = 1;
     __syncthreads();
     if (failed) break;  // block-uniform
-    layernorm_store(vals, nchunks, d, gamma, beta, eps, y + off, red);
+    layernorm_store(vals, nchunks, d, w, eps, y + off, red);
   }
   if (tid == 0) {
     if (failed) epoch_status[1] = (unsigned)DJV_ERR_TIMEOUT;
@@ -310,11 +315,13 @@ extern "C" int djv_allreduce_add_layernorm(djv_comm *c, void *y, void *r_out, co
               "allreduce_add_layernorm: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   c->last_stream = st;
-  djv::launch_kernel(allreduce_add_layernorm_kernel, 1, LN_THREADS, 0, st, c->bufs_dev, c->epoch_dev, c->rank,
-                     c->world, c->slot_bytes, static_cast<__half *>(y),
-      static_cast<__half *>(r_out), static_cast<const __half *>(partial),
-      static_cast<const __half *>(residual), static_cast<const __half *>(gamma),
-      static_cast<const __half *>(beta), B, d, eps);
+#define DJV_AR_CALL(NCH_)                                                                                       \
+  djv::launch_kernel(allreduce_add_layernorm_kernel<NCH_>, 1, LN_THREADS, 0, st, c->bufs_dev, c->epoch_dev,     \
+                     c->rank, c->world, c->slot_bytes, static_cast<__half *>(y), static_cast<__half *>(r_out), \
+                     static_cast<const __half *>(partial), static_cast<const __half *>(residual),              \
+                     static_cast<const __half *>(gamma), static_cast<const __half *>(beta), B, d, eps)
+  DJV_LN_DISPATCH(d / 8, DJV_AR_CALL);
+#undef DJV_AR_CALL
   count_launch();
   return check_launch("allreduce_add_layernorm");
 }

@@ -6,18 +6,23 @@
 
 namespace djv {
 
+template <int NCH>
 __global__ void __launch_bounds__(LN_THREADS)
 add_layernorm_kernel(__half *__restrict__ y, __half *r_out, const __half *__restrict__ x,
                      const __half *residual, const __half *__restrict__ xbias,
                      const __half *__restrict__ gamma, const __half *__restrict__ beta, int d, float eps) {
-  pdl_prologue();
   __shared__ float red[LN_THREADS / WARP];
   const int row = blockIdx.x, tid = threadIdx.x;
   const int nchunks = d / 8;
+  // the affine weights are fetched while the predecessor kernel may still be running
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  LnAffine<NCH> w;
+  ln_fetch_affine(w, gamma, beta, nchunks);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const size_t off = (size_t)row * d;
-  float vals[LN_MAX_CHUNKS][8];
+  float vals[NCH][8];
 #pragma unroll
-  for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int ch = c * LN_THREADS + tid;
     if (ch < nchunks) {
       float f[8], t[8];
@@ -40,7 +45,7 @@ add_layernorm_kernel(__half *__restrict__ y, __half *r_out, const __half *__rest
       for (int e = 0; e < 8; ++e) vals[c][e] = 0.f;
     }
   }
-  layernorm_store(vals, nchunks, d, gamma, beta, eps, y + off, red);
+  layernorm_store(vals, nchunks, d, w, eps, y + off, red);
 }
 
 }  // namespace djv
@@ -58,9 +63,13 @@ extern "C" int djv_add_layernorm(void *y, void *r_out, const void *x, const void
                   (!r_out || aligned16(r_out)) && (!residual || aligned16(residual)) &&
                   (!xbias || aligned16(xbias)),
               "add_layernorm: pointers must be 16-byte aligned");
-  djv::launch_kernel(add_layernorm_kernel, B, LN_THREADS, 0, static_cast<cudaStream_t>(stream), static_cast<__half *>(y), static_cast<__half *>(r_out), static_cast<const __half *>(x),
-      static_cast<const __half *>(residual), static_cast<const __half *>(xbias),
-      static_cast<const __half *>(gamma), static_cast<const __half *>(beta), d, eps);
+#define DJV_LN_CALL(NCH_)                                                                                      \
+  djv::launch_kernel(add_layernorm_kernel<NCH_>, B, LN_THREADS, 0, static_cast<cudaStream_t>(stream),          \
+                     static_cast<__half *>(y), static_cast<__half *>(r_out), static_cast<const __half *>(x),  \
+                     static_cast<const __half *>(residual), static_cast<const __half *>(xbias),               \
+                     static_cast<const __half *>(gamma), static_cast<const __half *>(beta), d, eps)
+  DJV_LN_DISPATCH(d / 8, DJV_LN_CALL);
+#undef DJV_LN_CALL
   count_launch();
   return check_launch("add_layernorm");
 }

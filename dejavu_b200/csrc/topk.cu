@@ -4,6 +4,7 @@
 // keys equal to T are needed; an ordered compaction then emits every index whose key is > T and the
 // lowest-index `need` entries whose key == T, in ascending index order. The result is therefore a
 // deterministic function of the scores: ties on the K-th score go to the lowest indices.
+#include "attn_state.cuh"
 #include "common.cuh"
 
 namespace djv {
@@ -69,7 +70,7 @@ __device__ __forceinline__ int block_exscan(int v, int *warp_sums, int *total) {
 template <typename T>
 __global__ void __launch_bounds__(TK_THREADS)
 topk_kernel(int32_t *__restrict__ idx32, int64_t *__restrict__ idx64, const T *__restrict__ scores,
-            int n, int K, int n_sub) {
+            int n, int K, int n_sub, int *attn_state, int attn_nheads, int attn_S) {
   pdl_prologue();
   using Key = typename KeyTraits<T>::Key;
   constexpr int BITS = KeyTraits<T>::BITS;
@@ -181,26 +182,24 @@ topk_kernel(int32_t *__restrict__ idx32, int64_t *__restrict__ idx64, const T *_
       }
     }
   }
+  // the selection just made is the head list of an attention layer: open that layer's decode step here
+  if (attn_state != nullptr) {
+    __syncthreads();  // idx32 is complete and visible to the whole block
+    attn_prep_block(attn_state, idx32, K, nullptr, nullptr, 0, attn_nheads, attn_S);
+  }
 }
 
 }  // namespace djv
 
 using namespace djv;
 
-extern "C" int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int n, int K,
-                        int score_is_f32, void *stream) {
-  DJV_REQUIRE(scores != nullptr, "topk: null scores");
-  DJV_REQUIRE(n >= 1, "topk: n=%d", n);
-  DJV_REQUIRE(K >= 0 && K <= n, "topk: K=%d outside [0,%d]", K, n);
-  if (K == 0) return DJV_OK;
-  DJV_REQUIRE(idx32 || idx64, "topk: no output pointer");
+static int launch_topk(int32_t *idx32, int64_t *idx64, const void *scores, int n, int K, int score_is_f32,
+                       int *attn_state, int nheads, int S, cudaStream_t st) {
   const size_t bytes = (size_t)n * (score_is_f32 ? 4 : 2);
   if (bytes > 200 * 1024) {
     set_error("topk: n=%d scores (%zu bytes) exceed the 200 KiB shared-memory budget", n, bytes);
     return DJV_ERR_UNSUPPORTED;
   }
-  if (K == 0) return DJV_OK;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   // Four histogram copies (one per 8 warps). One per warp was measured slower inside a decode step: this
   // block shares its multiprocessor with blocks of the main chain, and the extra shared-memory traffic of
   // 32 copies slowed those down enough to stretch the kernels they belong to.
@@ -209,18 +208,39 @@ extern "C" int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int 
   const size_t smem = ((bytes + 15) & ~(size_t)15) + (size_t)n_sub * 256 * sizeof(int);
   cudaError_t e;
   if (score_is_f32) {
-    e = cudaFuncSetAttribute(topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    e = cudaFuncSetAttribute(topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
     if (e == cudaSuccess)
-      djv::launch_kernel(topk_kernel<float>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const float *>(scores), n, K, n_sub);
+      djv::launch_kernel(topk_kernel<float>, 1, TK_THREADS, smem, st, idx32, idx64,
+                         static_cast<const float *>(scores), n, K, n_sub, attn_state, nheads, S);
   } else {
-    e = cudaFuncSetAttribute(topk_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    e = cudaFuncSetAttribute(topk_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
     if (e == cudaSuccess)
-      djv::launch_kernel(topk_kernel<__half>, 1, TK_THREADS, smem, st, idx32, idx64, static_cast<const __half *>(scores), n, K, n_sub);
+      djv::launch_kernel(topk_kernel<__half>, 1, TK_THREADS, smem, st, idx32, idx64,
+                         static_cast<const __half *>(scores), n, K, n_sub, attn_state, nheads, S);
   }
   if (e != cudaSuccess) {
-    set_error("topk: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    set_error("topk: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return DJV_ERR_CUDA;
   }
   count_launch();
   return check_launch("topk");
+}
+
+extern "C" int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int n, int K,
+                        int score_is_f32, void *stream) {
+  DJV_REQUIRE(scores != nullptr, "topk: null scores");
+  DJV_REQUIRE(n >= 1, "topk: n=%d", n);
+  DJV_REQUIRE(K >= 0 && K <= n, "topk: K=%d outside [0,%d]", K, n);
+  if (K == 0) return DJV_OK;
+  DJV_REQUIRE(idx32 || idx64, "topk: no output pointer");
+  return launch_topk(idx32, idx64, scores, n, K, score_is_f32, nullptr, 0, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int djv_topk_attn_prep(int32_t *idx32, const void *scores, int n, int K, int score_is_f32,
+                                  int32_t *state, int S, void *stream) {
+  DJV_REQUIRE(scores != nullptr && idx32 != nullptr && state != nullptr, "topk_attn_prep: null pointer");
+  DJV_REQUIRE(n >= 1 && n <= 1024, "topk_attn_prep: %d heads outside [1,1024]", n);
+  DJV_REQUIRE(K >= 1 && K <= n, "topk_attn_prep: K=%d outside [1,%d]", K, n);
+  DJV_REQUIRE(S >= 1, "topk_attn_prep: cache capacity S=%d", S);
+  return launch_topk(idx32, nullptr, scores, n, K, score_is_f32, state, n, S, static_cast<cudaStream_t>(stream));
 }

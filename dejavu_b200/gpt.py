@@ -160,6 +160,9 @@ class GPTModel(nn.Module):
                                                  process_group, **factory)
         self.layers = nn.ModuleList(
             [create_block(config, layer_idx=i, process_group=process_group, **factory) for i in range(config.n_layer)])
+        for a, b in zip(self.layers[:-1], self.layers[1:]):
+            if hasattr(a.mixer, "link_next"):
+                a.mixer.link_next(b.mixer)
         self.ln_f = nn.LayerNorm(config.hidden_size, eps=config.layer_norm_epsilon, **factory)
         self.att_sparse = getattr(config, "att_sparse", False)
         self.mlp_sparse = getattr(config, "mlp_sparse", False)

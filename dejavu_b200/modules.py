@@ -38,6 +38,8 @@ KV_WINDOW = _lib.KV_WINDOW
 # predictor + its top-K), forked from and joined to the main stream with events; inside a CUDA-graph
 # capture these become parallel branches of the graph. DJV_SIDE_STREAMS=0 keeps everything on one stream.
 SIDE_STREAMS_ENABLED = os.environ.get("DJV_SIDE_STREAMS", "1") != "0"
+# the kernel that selects the next layer's heads also opens that layer's decode step (development knob)
+FUSE_STEP_OPEN = os.environ.get("DJV_FUSE_STEP_OPEN", "1") != "0"
 _SIDE_STREAMS: dict = {}
 _SIDE_DIRTY: dict = {}  # device index -> names of side streams forked since the last join
 
@@ -305,6 +307,10 @@ class ParallelMHASparseAttMlp(nn.Module):
 
     sparse_attention = True
     run_predictor = True  # False: dense comparator mode, skip the look-ahead predictor
+    next_mixer = None  # the attention module of the following block (set by the model; not a submodule)
+
+    def link_next(self, mixer):
+        self.__dict__["next_mixer"] = mixer
 
     def __init__(self, embed_dim, num_heads, process_group, sp_kwargs, bias=True, dropout=0.0,
                  softmax_scale=None, causal=False, layer_idx=None, rotary_emb_dim=0, rotary_emb_scale_base=0,
@@ -397,10 +403,12 @@ class ParallelMHASparseAttMlp(nn.Module):
             head_idx = head_idx.contiguous()
             nnz = head_idx.numel()
         bias = self.Wqkv.bias
+        # the layer before may have opened this step already, in the kernel that selected the heads
+        step_is_open = 1 if (head_idx is not None and getattr(head_idx, "_step_opened_for", None) is self) else 0
         call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
              None if bias is None else bias.data_ptr(), xf.data_ptr(), b["x_ring"].data_ptr(), k_cache.data_ptr(),
              v_cache.data_ptr(), b["state"].data_ptr(), None if head_idx is None else head_idx.data_ptr(), nnz, d, n,
-             hd, S, st)
+             hd, S, step_is_open, st)
         if between is not None:
             between()
         call("djv_attn_step_attend", b["ctx"].data_ptr(), b["q"].data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
@@ -431,9 +439,20 @@ class ParallelMHASparseAttMlp(nn.Module):
 
         def predict_heads():
             if do_token_generation and self.sp is not None and self.run_predictor:
+                nxt = self.next_mixer if (decoding and FUSE_STEP_OPEN) else None
                 with _side(x, "att", after=residual) as done:
-                    result["att_idx"] = ops.topk_indices(self.sp(residual), self.att_k, torch.int32)
-                    done(result["att_idx"])
+                    scores = self.sp(residual)
+                    if nxt is not None and nxt.sparse_attention and scores.dim() == 1:
+                        # the selection is for the next layer's attention: open its decode step in the same
+                        # kernel, so that layer starts with its QKV projection
+                        S_next = inference_params.key_value_memory_dict[nxt.layer_idx][1].shape[2]
+                        state = nxt._decode_buffers(x.device, S_next)["state"]
+                        idx = ops.topk_indices_open_step(scores, self.att_k, state, S_next)
+                        idx._step_opened_for = nxt
+                    else:
+                        idx = ops.topk_indices(scores, self.att_k, torch.int32)
+                    result["att_idx"] = idx
+                    done(idx)
 
         if decoding:
             assert do_token_generation

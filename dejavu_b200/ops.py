@@ -285,6 +285,21 @@ def topk_indices(scores: torch.Tensor, k: int, dtype: torch.dtype = torch.int64)
     return out
 
 
+def topk_indices_open_step(scores: torch.Tensor, k: int, state: torch.Tensor, cache_len: int) -> torch.Tensor:
+    """topk_indices(scores, k, int32) over one score per head, fused with the head-selection half of the
+    decode step of the attention layer the selection is for: `state` is that layer's lazy-K/V state
+    (see djv_topk_attn_prep). The layer then runs its step with step_is_open = 1."""
+    assert scores.dim() == 1 and scores.dtype in (torch.float16, torch.float32)
+    n = scores.shape[0]
+    assert 1 <= k <= n <= 1024 and state.dtype == torch.int32
+    _require_cuda(scores, state)
+    scores = scores.contiguous()
+    out = torch.empty(k, dtype=torch.int32, device=scores.device)
+    call("djv_topk_attn_prep", out.data_ptr(), scores.data_ptr(), n, k, 1 if scores.dtype == torch.float32 else 0,
+         state.data_ptr(), cache_len, _stream())
+    return out
+
+
 def add_layernorm(x, residual, weight, bias, eps: float, xbias=None):
     """r = x + residual (+ xbias); y = LayerNorm(r). Returns (y, r). x, residual (batch, d) fp16.
     Stands in for `residual = dropped + residual; hidden = norm(residual)`

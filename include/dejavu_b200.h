@@ -196,7 +196,15 @@ int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, co
  * djv_attn_step_project = steps 1-2, djv_attn_step_attend = step 3 (q = the q_out of the first call). */
 int djv_attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x, void *x_ring,
                           void *k_cache, void *v_cache, int32_t *state, const int32_t *head_idx, int nnz,
-                          int d, int nheads, int hd, int S, void *stream);
+                          int d, int nheads, int hd, int S, int step_is_open, void *stream);
+/* Top-K of the head predictor's scores (one score per head of this rank) that also opens the decode step
+ * of the attention layer the selection is for: djv_topk(idx32, ...) followed by the head-selection half of
+ * step 1 above on `state`, in one launch, off the critical path (mha_dejavu.py:1364-1370 computes the
+ * selection for the next layer on a side stream). The x_ring[slot] = x half of step 1 is then done by
+ * djv_attn_step_project(..., step_is_open = 1, ...), which also skips its own step-1 launch; head_idx and
+ * nnz of that call are this call's idx32 and K. */
+int djv_topk_attn_prep(int32_t *idx32, const void *scores, int n, int K, int score_is_f32, int32_t *state,
+                       int S, void *stream);
 int djv_attn_step_attend(void *ctx, const void *q, const void *k_cache, const void *v_cache, int32_t *state,
                          int nheads, int hd, int S, float softmax_scale, void *scratch, size_t scratch_bytes,
                          void *stream);

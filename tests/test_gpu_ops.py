@@ -343,7 +343,8 @@ def test_add_layernorm_vs_oracle(cuda, B, d):
 @pytest.mark.parametrize("nheads,hd,d,P,steps,nsel", [(6, 32, 256, 5, 37, 2), (12, 128, 1536, 40, 35, 4),
                                                        (9, 128, 1152, 130, 20, 3)])
 @pytest.mark.parametrize("rpb", [0, 32, 16, 8, 1])  # rows per block of the QKV kernel; 32, 16, 8: tensor cores
-def test_attn_step_state_machine_vs_oracle(cuda, monkeypatch, nheads, hd, d, P, steps, nsel, rpb):
+@pytest.mark.parametrize("opened", [False, True])  # True: the top-K kernel opens the step (djv_topk_attn_prep)
+def test_attn_step_state_machine_vs_oracle(cuda, monkeypatch, nheads, hd, d, P, steps, nsel, rpb, opened):
     from dejavu_b200 import _lib
 
     if rpb:
@@ -379,10 +380,23 @@ def test_attn_step_state_machine_vs_oracle(cuda, monkeypatch, nheads, hd, d, P, 
         ctx_o, heads = O.attn_sparse_step(state_o, x, ring_o, Wqkv, bqkv, k_ref, v_ref,
                                           None if dense_step else sel.tolist(), scale)
         xd, seld = x.to(cuda), sel.to(cuda)
-        _lib.call("djv_attn_step", ctx_d.data_ptr(), q_d.data_ptr(), Wd.data_ptr(), bd.data_ptr(), xd.data_ptr(),
-                  ring_d.data_ptr(), k_dev.data_ptr(), v_dev.data_ptr(), state_d.data_ptr(),
-                  None if dense_step else seld.data_ptr(), nsel, d, nheads, hd, S, scale, scratch.data_ptr(),
-                  scratch.numel(), st)
+        if opened and not dense_step:
+            scores = torch.zeros(nheads, dtype=torch.float16)
+            scores[sel.long()] = 1.0 + torch.rand(nsel, generator=gen).half()
+            seld = torch.full((nsel,), -1, dtype=torch.int32, device=cuda)
+            _lib.call("djv_topk_attn_prep", seld.data_ptr(), scores.to(cuda).data_ptr(), nheads, nsel, 0,
+                      state_d.data_ptr(), S, st)
+            assert seld.cpu().tolist() == sorted(sel.tolist())
+            _lib.call("djv_attn_step_project", q_d.data_ptr(), Wd.data_ptr(), bd.data_ptr(), xd.data_ptr(),
+                      ring_d.data_ptr(), k_dev.data_ptr(), v_dev.data_ptr(), state_d.data_ptr(), seld.data_ptr(),
+                      nsel, d, nheads, hd, S, 1, st)
+            _lib.call("djv_attn_step_attend", ctx_d.data_ptr(), q_d.data_ptr(), k_dev.data_ptr(), v_dev.data_ptr(),
+                      state_d.data_ptr(), nheads, hd, S, scale, scratch.data_ptr(), scratch.numel(), st)
+        else:
+            _lib.call("djv_attn_step", ctx_d.data_ptr(), q_d.data_ptr(), Wd.data_ptr(), bd.data_ptr(),
+                      xd.data_ptr(), ring_d.data_ptr(), k_dev.data_ptr(), v_dev.data_ptr(), state_d.data_ptr(),
+                      None if dense_step else seld.data_ptr(), nsel, d, nheads, hd, S, scale, scratch.data_ptr(),
+                      scratch.numel(), st)
         sd = state_d.cpu().tolist()
         n_eff = sd[2]
         assert sd[3] == 0
