@@ -47,6 +47,16 @@ class TensorParallelComm:
                                                           self.slot_bytes))
         # every rank has mapped every buffer and initialised its own before the first call
         dist.barrier(group=process_group)
+        self._pushed = set()  # data_ptr of placeholders whose content a producer kernel has sent already
+
+    @property
+    def handle(self):
+        return self._comm
+
+    def note_pushed(self, placeholder: torch.Tensor):
+        """The kernel that produced this rank's partial has stored it into every rank's receive buffer;
+        `placeholder` (never written) stands for it until allreduce_add_layernorm consumes it."""
+        self._pushed.add(placeholder.data_ptr())
 
     def allreduce_add_layernorm(self, partial, residual, weight, bias, eps):
         """r = sum over ranks(partial) + residual; y = LayerNorm(r). partial, residual (B, d) fp16.
@@ -54,7 +64,10 @@ class TensorParallelComm:
         B, d = partial.shape
         partial = partial.contiguous()
         y, r = torch.empty_like(partial), torch.empty_like(partial)
-        call("djv_allreduce_add_layernorm", self._comm, y.data_ptr(), r.data_ptr(), partial.data_ptr(),
+        sent = partial.data_ptr() in self._pushed
+        self._pushed.discard(partial.data_ptr())
+        call("djv_allreduce_add_layernorm", self._comm, y.data_ptr(), r.data_ptr(),
+             None if sent else partial.data_ptr(),
              None if residual is None else residual.contiguous().data_ptr(), weight.data_ptr(), bias.data_ptr(),
              B, d, float(eps), torch.cuda.current_stream().cuda_stream)
         return y, r

@@ -12,6 +12,7 @@
 
 #include "attn_state.cuh"
 #include "common.cuh"
+#include "push.cuh"
 #include "rowdot_mma.cuh"
 
 namespace djv {
@@ -557,7 +558,7 @@ template <int HD, int B>
 __global__ void __launch_bounds__(OP_THREADS)
 out_proj_sparse_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                        const int *__restrict__ head_idx, const int *__restrict__ n_active_dev,
-                       const __half *__restrict__ bias, int d, int nheads, int nnz) {
+                       const __half *__restrict__ bias, int d, int nheads, int nnz, PushTarget push) {
   pdl_prologue();
   constexpr int LPS = HD / 8;      // lanes per segment
   constexpr int SEGS = WARP / LPS; // segments per warp load
@@ -610,13 +611,28 @@ out_proj_sparse_kernel(__half *__restrict__ Y, const __half *__restrict__ W, con
 #pragma unroll
     for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
   if (lane == 0) {
+    if (push.bufs != nullptr) {
+      // this rank's partial goes straight into every rank's receive buffer, 4 rows (8 bytes) at a time;
+      // d % 4 == 0, so the warp's 4 rows are all inside or all outside
+      static_assert(OP_ROWS == 4, "the push path packs 4 rows into one 8-byte store");
+      const size_t piece = push_piece_offset(push);
 #pragma unroll
-    for (int r = 0; r < OP_ROWS; ++r) {
-      const int n = n0 + r;
-      if (n < d) {
-        const float bv = bias ? __half2float(bias[n]) : 0.f;
+      for (int b = 0; b < B; ++b) {
+        float v[OP_ROWS];
 #pragma unroll
-        for (int b = 0; b < B; ++b) Y[(size_t)b * d + n] = __float2half_rn(acc[r][b] + bv);
+        for (int r = 0; r < OP_ROWS; ++r) v[r] = acc[r][b] + (bias ? __half2float(bias[n0 + r]) : 0.f);
+        __half2 o[2] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3])};
+        push8(push, piece, (size_t)b * d + n0, *reinterpret_cast<uint2 *>(o));
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < OP_ROWS; ++r) {
+        const int n = n0 + r;
+        if (n < d) {
+          const float bv = bias ? __half2float(bias[n]) : 0.f;
+#pragma unroll
+          for (int b = 0; b < B; ++b) Y[(size_t)b * d + n] = __float2half_rn(acc[r][b] + bv);
+        }
       }
     }
   }
@@ -713,11 +729,11 @@ extern "C" int djv_qkv_proj_sparse(void *y, const void *w, const void *x, const 
 template <int HD>
 static int launch_out_proj(int B, __half *Y, const __half *W, const __half *X, const int *head_idx,
                            const int *n_active_dev, const __half *bias, int d, int nheads, int nnz,
-                           cudaStream_t st) {
+                           cudaStream_t st, const PushTarget &push = PushTarget{}) {
   const int warps = ceil_div(d, OP_ROWS);
   const int grid = ceil_div(warps * WARP, OP_THREADS);
 #define DJV_OP(B_) \
-  djv::launch_kernel(out_proj_sparse_kernel<HD, B_>, grid, OP_THREADS, 0, st, Y, W, X, head_idx, n_active_dev, bias, d, nheads, nnz)
+  djv::launch_kernel(out_proj_sparse_kernel<HD, B_>, grid, OP_THREADS, 0, st, Y, W, X, head_idx, n_active_dev, bias, d, nheads, nnz, push)
   switch (B) {
     case 1: DJV_OP(1); break;
     case 2: DJV_OP(2); break;
@@ -752,6 +768,32 @@ extern "C" int djv_out_proj_sparse(void *y, const void *w, const void *x, const 
     count_launch();
   }
   return check_launch("out_proj_sparse");
+}
+
+// The same projection with the result sent into every rank's receive buffer of the tensor-parallel exchange
+// instead of y (see push.cuh): the NVLink trip overlaps the kernel's tail, and the all-reduce kernel that
+// follows is called with partial == NULL.
+extern "C" int djv_out_proj_sparse_push(djv_comm *comm, const void *w, const void *x, const int32_t *head_idx,
+                                        const int32_t *n_active_dev, const void *bias, int B, int d,
+                                        int nheads, int hd, int nnz, void *stream) {
+  DJV_REQUIRE(comm && w && x && (head_idx || nnz == 0), "out_proj_sparse_push: null pointer");
+  int rc = check_hd("out_proj_sparse_push", hd, d);
+  if (rc) return rc;
+  DJV_REQUIRE(B >= 1 && B <= 4, "out_proj_sparse_push: batch %d outside [1,4]", B);
+  DJV_REQUIRE((size_t)B * d * 2 <= comm->slot_bytes, "out_proj_sparse_push: %zu bytes exceed the slot (%zu)",
+              (size_t)B * d * 2, comm->slot_bytes);
+  DJV_REQUIRE(nnz >= 0 && nnz <= nheads, "out_proj_sparse_push: nnz=%d outside [0,%d]", nnz, nheads);
+  DJV_REQUIRE(aligned16(w) && aligned16(x), "out_proj_sparse_push: w and x must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __half *W = static_cast<const __half *>(w), *X = static_cast<const __half *>(x);
+  const __half *bi = static_cast<const __half *>(bias);
+  const PushTarget push = push_target(comm);
+  if (hd == 128) rc = launch_out_proj<128>(B, nullptr, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st, push);
+  else if (hd == 64) rc = launch_out_proj<64>(B, nullptr, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st, push);
+  else rc = launch_out_proj<32>(B, nullptr, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st, push);
+  if (rc) return rc;
+  count_launch();
+  return check_launch("out_proj_sparse_push");
 }
 
 static int cache_copy(bool is_k, const void *src, void *cache, const int32_t *head_idx,

@@ -17,52 +17,16 @@
 // No multicast / multimem objects are used: a peer that exits between steps cannot fault the others,
 // their next call just runs out its wait and reports DJV_ERR_TIMEOUT in the status word.
 #include "norm.cuh"
-
-struct djv_comm {
-  int rank, world;
-  size_t slot_bytes;
-  // device-side tables (cudaMalloc'ed by djv_comm_create)
-  void **bufs_dev;
-  unsigned *epoch_dev;  // [0] epoch, [1] status
-  cudaStream_t last_stream;
-};
+#include "push.cuh"
 
 namespace djv {
 
-constexpr int AR_MAX_WORLD = 8;
-constexpr int AR_SLOTS = 3;
-constexpr unsigned AR_SENTINEL2 = 0x80008000u;  // two fp16 -0.0
 constexpr unsigned long long AR_WAIT_LIMIT_NS = 2000ull * 1000 * 1000;  // a wait on a peer gives up after 2 s
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
-}
-
-__device__ __forceinline__ void st_sys16(void *p, const uint4 &v) {
-  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
-__device__ __forceinline__ uint4 ld_sys16(const void *p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-// -0.0 halves become +0.0
-__device__ __forceinline__ unsigned no_sentinel2(unsigned w) {
-  if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;
-  if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
-  return w;
-}
-__device__ __forceinline__ bool has_sentinel2(unsigned w) {
-  return (w & 0xffffu) == 0x8000u || (w >> 16) == 0x8000u;
-}
-__device__ __forceinline__ bool arrived16(const uint4 &v) {
-  return !(has_sentinel2(v.x) || has_sentinel2(v.y) || has_sentinel2(v.z) || has_sentinel2(v.w));
 }
 
 __global__ void fill_sentinel_kernel(uint4 *p, size_t n16) {
@@ -97,7 +61,8 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restr
   const size_t old_off = (size_t)((epoch + 2) % AR_SLOTS) * world * slot_bytes;
 
   // 1. push this rank's partial into piece [rank] of the current slot of every rank
-  {
+  //    (partial == nullptr: the kernel that produced it has pushed it already, see push.cuh)
+  if (partial != nullptr) {
     void *dst[AR_MAX_WORLD];
 #pragma unroll
     for (int p = 0; p < AR_MAX_WORLD; ++p)
@@ -127,6 +92,14 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restr
   for (int row = 0; row < B; ++row) {
     const size_t off = (size_t)row * d;
     float vals[NCH][8];
+    // the residual row is requested before the wait on the peers, not after it
+    uint4 rres[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int ch = c * LN_THREADS + tid;
+      rres[c] = (residual && ch < nchunks) ? *reinterpret_cast<const uint4 *>(residual + off + (size_t)ch * 8)
+                                           : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       const int ch = c * LN_THREADS + tid;
@@ -160,7 +133,7 @@ allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restr
         }
         round_store8(f, nullptr);  // the all-reduced activation is an fp16 tensor
         if (residual) {
-          unpack8(*reinterpret_cast<const uint4 *>(residual + off + (size_t)ch * 8), t);
+          unpack8(rres[c], t);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] += t[e];
         }
@@ -305,12 +278,12 @@ extern "C" int djv_comm_status(djv_comm *c) {
 extern "C" int djv_allreduce_add_layernorm(djv_comm *c, void *y, void *r_out, const void *partial,
                                            const void *residual, const void *gamma, const void *beta,
                                            int B, int d, float eps, void *stream) {
-  DJV_REQUIRE(c && y && partial && gamma && beta, "allreduce_add_layernorm: null pointer");
+  DJV_REQUIRE(c && y && gamma && beta, "allreduce_add_layernorm: null pointer");
   DJV_REQUIRE(B >= 1 && d >= 8 && d % 8 == 0 && d / 8 <= LN_THREADS * LN_MAX_CHUNKS,
               "allreduce_add_layernorm: bad B=%d d=%d", B, d);
   DJV_REQUIRE((size_t)B * d * 2 <= c->slot_bytes, "allreduce_add_layernorm: %zu bytes exceed the slot (%zu)",
               (size_t)B * d * 2, c->slot_bytes);
-  DJV_REQUIRE(aligned16(y) && aligned16(partial) && aligned16(gamma) && aligned16(beta) &&
+  DJV_REQUIRE(aligned16(y) && (!partial || aligned16(partial)) && aligned16(gamma) && aligned16(beta) &&
                   (!r_out || aligned16(r_out)) && (!residual || aligned16(residual)),
               "allreduce_add_layernorm: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -316,6 +316,33 @@ extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x,
   return check_launch("gather_transposed_gemv");
 }
 
+// fc2 with the result sent into every rank's receive buffer of the tensor-parallel exchange instead of y
+// (see push.cuh); the all-reduce kernel that follows is called with partial == NULL.
+extern "C" int djv_gather_transposed_gemv_push(djv_comm *comm, const void *w, const void *x, const void *idx,
+                                               const void *bias, int B, int N, int M, long long ldw,
+                                               int idx_is_64, void *scratch, size_t scratch_bytes,
+                                               void *stream) {
+  DJV_REQUIRE(comm != nullptr, "gather_transposed_gemv_push: null comm");
+  DJV_REQUIRE(M >= 1, "gather_transposed_gemv_push: needs at least one row");
+  int rc = check_common("gather_transposed_gemv_push", w /* y unused */, w, x, B, N, M, ldw);
+  if (rc) return rc;
+  DJV_REQUIRE(B <= RA_MAX_B, "gather_transposed_gemv_push: batch %d above %d", B, RA_MAX_B);
+  DJV_REQUIRE((size_t)B * N * 2 <= comm->slot_bytes, "gather_transposed_gemv_push: %zu bytes exceed the slot (%zu)",
+              (size_t)B * N * 2, comm->slot_bytes);
+  DJV_REQUIRE(bias == nullptr || aligned16(bias), "gather_transposed_gemv_push: bias must be 16-byte aligned");
+  const size_t need = djv_gather_transposed_gemv_scratch_bytes(B, N, M);
+  if (scratch == nullptr || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
+    set_error("gather_transposed_gemv_push: scratch needs %zu bytes, 256-byte aligned (got %zu)", need, scratch_bytes);
+    return DJV_ERR_SCRATCH;
+  }
+  rc = rowaxpy_slice(B, nullptr, static_cast<const __half *>(w), static_cast<const __half *>(x), idx,
+                     static_cast<const __half *>(bias), scratch, M, N, ldw, idx_is_64,
+                     static_cast<cudaStream_t>(stream), push_target(comm));
+  if (rc) return rc;
+  count_launch();
+  return check_launch("gather_transposed_gemv_push");
+}
+
 extern "C" int djv_mlp_sparse(void *y, void *h, const void *w1, const void *w2t, const void *x,
                               const void *idx, const void *bias1, const void *bias2, int B, int N,
                               int M, long long ldw1, long long ldw2t, int idx_is_64, void *scratch,

@@ -13,6 +13,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "push.cuh"
 
 namespace djv {
 
@@ -31,7 +32,7 @@ __global__ void __cluster_dims__(1, RA_CLUSTER, 1) __launch_bounds__(RA_THREADS)
 rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                const void *__restrict__ idx, const __half *__restrict__ bias,
                float *__restrict__ partial, unsigned *__restrict__ counters, int M, int N,
-               long long ldw, int idx64, int rows_per_warp) {
+               long long ldw, int idx64, int rows_per_warp, PushTarget push) {
   pdl_prologue();
   constexpr int RA_COLS = WARP * 8 * CW;           // columns per block
   constexpr int RA_SLICE = RA_COLS / RA_CLUSTER;   // columns a block finishes
@@ -147,24 +148,50 @@ rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __hal
   }
   cluster.sync();  // after this no block reads another block's shared memory any more
 
+  // a thread finishes 8 consecutive columns: one 16-byte store to Y, or to every rank's receive buffer
   const int gcol0 = tile * RA_COLS + crank * RA_SLICE;
-  if (tid < RA_SLICE * B) {
-    const int b = tid / RA_SLICE, col = tid % RA_SLICE;
-    float s = 0.f;
+  constexpr int G8 = RA_SLICE / 8;
+  const int fb = tid / G8, fg = tid % G8;  // valid when tid < G8 * B
+  const int gcol = gcol0 + fg * 8;         // N % 8 == 0: the 8 columns are all inside or all outside
+  const bool finisher = tid < G8 * B && gcol < N;
+  auto emit = [&](float (&v)[8]) {
+    if (bias) {
+      float t8[8];
+      const uint4 bv = ld_cached16(bias + gcol);
+      const float2 b0 = h2f(bv.x), b1 = h2f(bv.y), b2 = h2f(bv.z), b3 = h2f(bv.w);
+      t8[0] = b0.x; t8[1] = b0.y; t8[2] = b1.x; t8[3] = b1.y; t8[4] = b2.x; t8[5] = b2.y; t8[6] = b3.x; t8[7] = b3.y;
 #pragma unroll
-    for (int src = 0; src < RA_CLUSTER; ++src) s += fin[src][b][col];
-    const int gcol = gcol0 + col;
-    if (gcol < N) {
-      if (MCC == 1) {
-        Y[(size_t)b * N + gcol] = __float2half_rn(s + (bias ? __half2float(bias[gcol]) : 0.f));
-      } else {
-        __stcg(partial + ((size_t)mcc * B + b) * N + gcol, s);
-      }
+      for (int e = 0; e < 8; ++e) v[e] += t8[e];
+    }
+    __half2 o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+    const uint4 packed = *reinterpret_cast<uint4 *>(o);
+    if (push.bufs != nullptr)
+      push16(push, push_piece_offset(push), (size_t)fb * N + gcol, packed);
+    else
+      *reinterpret_cast<uint4 *>(Y + (size_t)fb * N + gcol) = packed;
+  };
+  if (finisher) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float sum = 0.f;
+#pragma unroll
+      for (int src = 0; src < RA_CLUSTER; ++src) sum += fin[src][fb][fg * 8 + e];
+      v[e] = sum;
+    }
+    if (MCC == 1) {
+      emit(v);
+    } else {
+      float4 *dst = reinterpret_cast<float4 *>(partial + ((size_t)mcc * B + fb) * N + gcol);
+      __stcg(dst, make_float4(v[0], v[1], v[2], v[3]));
+      __stcg(dst + 1, make_float4(v[4], v[5], v[6], v[7]));
     }
   }
   if (MCC == 1) return;
 
-  // several clusters per column tile: the last block to arrive for this 32-column slice adds them
+  // several clusters per column tile: the last block to arrive for this slice of columns adds them
   __threadfence();
   __syncthreads();
   const int counter_id = tile * RA_CLUSTER + crank;
@@ -175,14 +202,17 @@ rowaxpy_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __hal
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  if (tid < RA_SLICE * B) {
-    const int b = tid / RA_SLICE, col = tid % RA_SLICE;
-    const int gcol = gcol0 + col;
-    if (gcol < N) {
-      float s = 0.f;
-      for (int c = 0; c < MCC; ++c) s += __ldcg(partial + ((size_t)c * B + b) * N + gcol);
-      Y[(size_t)b * N + gcol] = __float2half_rn(s + (bias ? __half2float(bias[gcol]) : 0.f));
+  if (finisher) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    for (int c = 0; c < MCC; ++c) {
+      const float4 *src = reinterpret_cast<const float4 *>(partial + ((size_t)c * B + fb) * N + gcol);
+      const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
     }
+    emit(v);
   }
   if (tid == 0) counters[counter_id] = 0;  // ready for the next launch
 }
@@ -259,20 +289,20 @@ inline size_t rowaxpy_scratch_bytes(int B, int N, int M) {
 template <int B>
 inline void launch_rowaxpy(const RowaxpyPlan &p, __half *Y, const __half *W, const __half *X,
                            const void *idx, const __half *bias, float *partial, unsigned *counters,
-                           int M, int N, long long ldw, int idx64, cudaStream_t st) {
+                           int M, int N, long long ldw, int idx64, cudaStream_t st, const PushTarget &push) {
   dim3 grid(p.tiles, p.mcc * RA_CLUSTER);
   if (p.cw == 2 && B <= 2)
     djv::launch_kernel(rowaxpy_kernel<(B <= 2 ? B : 1), 2>, grid, RA_THREADS, 0, st, Y, W, X, idx, bias, partial,
-                       counters, M, N, ldw, idx64, p.rpw);
+                       counters, M, N, ldw, idx64, p.rpw, push);
   else
     djv::launch_kernel(rowaxpy_kernel<B, 1>, grid, RA_THREADS, 0, st, Y, W, X, idx, bias, partial, counters, M, N,
-                       ldw, idx64, p.rpw);
+                       ldw, idx64, p.rpw, push);
 }
 
 // B <= RA_MAX_B rows of x per launch
 inline int rowaxpy_slice(int B, __half *Y, const __half *W, const __half *X, const void *idx,
                          const __half *bias, void *scratch, int M, int N, long long ldw, int idx64,
-                         cudaStream_t st) {
+                         cudaStream_t st, const PushTarget &push = PushTarget{}) {
   const RowaxpyPlan p = plan_rowaxpy(M, N, B);
   if ((size_t)p.tiles * RA_CLUSTER * sizeof(unsigned) > RA_COUNTER_BYTES) {
     set_error("gather_transposed_gemv: N=%d needs more block counters than the scratch header holds", N);
@@ -281,10 +311,10 @@ inline int rowaxpy_slice(int B, __half *Y, const __half *W, const __half *X, con
   unsigned *counters = reinterpret_cast<unsigned *>(scratch);
   float *partial = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + RA_COUNTER_BYTES);
   switch (B) {
-    case 1: launch_rowaxpy<1>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
-    case 2: launch_rowaxpy<2>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
-    case 3: launch_rowaxpy<3>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
-    case 4: launch_rowaxpy<4>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st); break;
+    case 1: launch_rowaxpy<1>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st, push); break;
+    case 2: launch_rowaxpy<2>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st, push); break;
+    case 3: launch_rowaxpy<3>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st, push); break;
+    case 4: launch_rowaxpy<4>(p, Y, W, X, idx, bias, partial, counters, M, N, ldw, idx64, st, push); break;
     default: set_error("gather_transposed_gemv: internal batch slice %d", B); return DJV_ERR_INVALID;
   }
   return DJV_OK;

@@ -40,6 +40,8 @@ KV_WINDOW = _lib.KV_WINDOW
 SIDE_STREAMS_ENABLED = os.environ.get("DJV_SIDE_STREAMS", "1") != "0"
 # the kernel that selects the next layer's heads also opens that layer's decode step (development knob)
 FUSE_STEP_OPEN = os.environ.get("DJV_FUSE_STEP_OPEN", "1") != "0"
+# fc2 and out_proj send their result into the peers' receive buffers themselves (development knob)
+PUSH_PARTIALS = os.environ.get("DJV_PUSH_PARTIALS", "1") != "0"
 _SIDE_STREAMS: dict = {}
 _SIDE_DIRTY: dict = {}  # device index -> names of side streams forked since the last join
 
@@ -224,6 +226,7 @@ class ParallelFusedMLPDejavu(nn.Module):
     has_predictor = True
     run_predictor = True         # False: dense comparator mode, skip the look-ahead predictor
     dense_decode_cublas = False  # True: dense decode GEMVs through torch (cuBLAS)
+    push_comm = None             # TensorParallelComm: fc2 sends its result to the peers itself
 
     def __init__(self, in_features, hidden_features, sp_kwargs, out_features=None, activation="gelu_approx",
                  layer_idx=None, process_group=None, bias1=True, bias2=True, sequence_parallel=True,
@@ -263,12 +266,13 @@ class ParallelFusedMLPDejavu(nn.Module):
             assert x.size(1) == 1
             assert self.activation == "relu", "the sparse path applies ReLU (gather_gemv.py:655)"
             out = ops.mlp_sparse(x.view(x.size(0), -1), self.fc1.weight, self.fc2.weight_t, idx, self.fc1.bias,
-                                 self.fc2.bias)
+                                 self.fc2.bias, push_comm=self.push_comm)
             out = out.view(x.size(0), 1, -1)
         elif do_token_generation and not self.dense_decode_cublas:
             act = "relu" if self.activation == "relu" else "gelu_approx"
             h = ops.dense_gemv(x.view(x.size(0), -1), self.fc1.weight, self.fc1.bias, act)
-            out = ops.dense_transposed_gemv(h, self.fc2.weight_t, self.fc2.bias).view(x.size(0), 1, -1)
+            out = ops.dense_transposed_gemv(h, self.fc2.weight_t, self.fc2.bias,
+                                            push_comm=self.push_comm).view(x.size(0), 1, -1)
         else:
             h = F.linear(x, self.fc1.weight, self.fc1.bias)
             h = F.relu(h) if self.activation == "relu" else F.gelu(h, approximate="tanh")
@@ -308,6 +312,7 @@ class ParallelMHASparseAttMlp(nn.Module):
     sparse_attention = True
     run_predictor = True  # False: dense comparator mode, skip the look-ahead predictor
     next_mixer = None  # the attention module of the following block (set by the model; not a submodule)
+    push_comm = None   # TensorParallelComm: out_proj sends its result to the peers itself
 
     def link_next(self, mixer):
         self.__dict__["next_mixer"] = mixer
@@ -419,8 +424,14 @@ class ParallelMHASparseAttMlp(nn.Module):
         state = b["state"]
         eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
         n_eff_ptr = state.data_ptr() + 4 * 2
-        call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
-             eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
+        if self.push_comm is not None:
+            call("djv_out_proj_sparse_push", self.push_comm.handle, self.out_proj.weight.data_ptr(),
+                 b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd,
+                 n, st)
+            self.push_comm.note_pushed(out)
+        else:
+            call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
+                 eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
         # the window advance is folded into the next step's first kernel (no djv_attn_step_finish launch)
         return out.view(1, 1, d)
 
@@ -518,6 +529,9 @@ class BlockMlpAttSparse(nn.Module):
         self.comm = comm
         self.mixer.skip_all_reduce = comm is not None
         self.mlp.skip_all_reduce = comm is not None
+        push = comm if PUSH_PARTIALS else None
+        self.mixer.__dict__["push_comm"] = push
+        self.mlp.__dict__["push_comm"] = push
 
     def _add_norm(self, hidden_states, residual, norm, reduce_first):
         """residual = hidden + residual; hidden = norm(residual); `hidden` may still be a rank-partial sum."""

@@ -104,9 +104,13 @@ def gather_transposed_gemv(
     weight: torch.Tensor,
     idx: torch.Tensor,
     bias: Optional[torch.Tensor] = None,
+    push_comm=None,
 ) -> torch.Tensor:
     """y = weight[idx, :]^T @ x + bias;  x (batch, M), weight (Z, N), idx (M,), bias (N,) -> (batch, N).
-    Deterministic (fixed summation order), unlike the reference's atomic-add kernel."""
+    Deterministic (fixed summation order), unlike the reference's atomic-add kernel.
+    With `push_comm` (a TensorParallelComm) the result is not written to the returned tensor but sent into
+    every rank's receive buffer of the exchange; the returned tensor is a placeholder that
+    push_comm.allreduce_add_layernorm recognises."""
     Z, N = weight.shape
     (M,) = idx.shape
     batch, _ = x.shape
@@ -126,12 +130,18 @@ def gather_transposed_gemv(
     output = torch.empty(batch, N, device=x.device, dtype=x.dtype)
     need = _lib.load().djv_gather_transposed_gemv_scratch_bytes(batch, N, M)
     scratch = _scratch(need, x.device)
+    if push_comm is not None and M >= 1 and batch <= 4:
+        call("djv_gather_transposed_gemv_push", push_comm.handle, weight.data_ptr(), x.data_ptr(), idx.data_ptr(),
+             _ptr(bias), batch, N, M, weight.stride(0), idx64, scratch.data_ptr(), scratch.numel(), _stream())
+        push_comm.note_pushed(output)
+        return output
     call("djv_gather_transposed_gemv", output.data_ptr(), weight.data_ptr(), x.data_ptr(), idx.data_ptr(),
          _ptr(bias), batch, N, M, weight.stride(0), idx64, scratch.data_ptr(), scratch.numel(), _stream())
     return output
 
 
-def dense_transposed_gemv(x: torch.Tensor, weight_t: torch.Tensor, bias: Optional[torch.Tensor] = None):
+def dense_transposed_gemv(x: torch.Tensor, weight_t: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                          push_comm=None):
     """y = x @ weight_t + bias with weight_t (M, N) contiguous (a transposed Linear weight), same kernel
     as gather_transposed_gemv with the identity index list."""
     M, N = weight_t.shape
@@ -143,15 +153,20 @@ def dense_transposed_gemv(x: torch.Tensor, weight_t: torch.Tensor, bias: Optiona
     output = torch.empty(batch, N, device=x.device, dtype=x.dtype)
     need = _lib.load().djv_gather_transposed_gemv_scratch_bytes(batch, N, M)
     scratch = _scratch(need, x.device)
+    if push_comm is not None and batch <= 4:
+        call("djv_gather_transposed_gemv_push", push_comm.handle, weight_t.data_ptr(), x.data_ptr(), None,
+             _ptr(bias), batch, N, M, weight_t.stride(0), 0, scratch.data_ptr(), scratch.numel(), _stream())
+        push_comm.note_pushed(output)
+        return output
     call("djv_gather_transposed_gemv", output.data_ptr(), weight_t.data_ptr(), x.data_ptr(), None, _ptr(bias),
          batch, N, M, weight_t.stride(0), 0, scratch.data_ptr(), scratch.numel(), _stream())
     return output
 
 
-def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None):
+def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None, push_comm=None):
     """x (batch, d); W1 (4d, d); W2t (4d, d) = W2 transposed, contiguous; bias1 (4d); bias2 (d)."""
     x = gather_gemv(x, W1, idx, bias1, activation="relu")
-    x = gather_transposed_gemv(x, W2t, idx, bias2)
+    x = gather_transposed_gemv(x, W2t, idx, bias2, push_comm=push_comm)
     return x
 
 

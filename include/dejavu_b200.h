@@ -261,7 +261,18 @@ int djv_comm_create(djv_comm **out, int rank, int world, void *const *bufs, size
 int djv_comm_destroy(djv_comm *comm);
 /* Reads the device status word (synchronises the stream the comm last ran on). */
 int djv_comm_status(djv_comm *comm);
-/* partial: this rank's (B,d) fp16 partial sums. B*d*2 <= slot_bytes. */
+/* The two producers of a rank's partial sums can send them into every rank's receive buffer themselves, as
+ * they finish each piece, so that the NVLink trip overlaps their tail and the launch of the all-reduce:
+ * same arguments as djv_gather_transposed_gemv / djv_out_proj_sparse with `comm` in place of y (B <= 4,
+ * B*N*2 <= slot_bytes). The djv_allreduce_add_layernorm call that follows passes partial = NULL.
+ * Exactly one producer call per all-reduce call, on the same stream, before it. */
+int djv_gather_transposed_gemv_push(djv_comm *comm, const void *w, const void *x, const void *idx,
+                                    const void *bias, int B, int N, int M, long long ldw, int idx_is_64,
+                                    void *scratch, size_t scratch_bytes, void *stream);
+int djv_out_proj_sparse_push(djv_comm *comm, const void *w, const void *x, const int32_t *head_idx,
+                             const int32_t *n_active_dev, const void *bias, int B, int d, int nheads, int hd,
+                             int nnz, void *stream);
+/* partial: this rank's (B,d) fp16 partial sums, or NULL when a *_push call has sent them. B*d*2 <= slot_bytes. */
 int djv_allreduce_add_layernorm(djv_comm *comm, void *y, void *r_out, const void *partial,
                                 const void *residual, const void *gamma, const void *beta, int B,
                                 int d, float eps, void *stream);

@@ -505,3 +505,66 @@ def test_allreduce_wait_runs_out_and_reports(cuda):
     # the context is still usable
     assert torch.equal((x + 1).cpu(), x.cpu() + 1)
     lib.djv_comm_destroy(comm)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_push_producers_feed_the_allreduce(cuda, world):
+    """fc2 and out_proj store their result straight into every rank's receive buffer; the all-reduce that
+    follows (partial = NULL) finds this rank's piece there. Peers' pieces are written by the test."""
+    from dejavu_b200 import _lib, ops
+
+    lib = _lib.load()
+    d, M, Z, nheads, hd = 1024, 96, 512, 4, 128
+    slot_bytes = d * 2
+    comm, bufs_t = _make_comm(lib, cuda, world, slot_bytes)
+    own = bufs_t[0].view(3, world, d)
+    gen = torch.Generator().manual_seed(world)
+    gamma, beta = (1 + rand(gen, (d,), 0.1)).to(cuda), rand(gen, (d,), 0.1).to(cuda)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def finish(step, mine, res):
+        """pre-fill the peers' pieces, run the all-reduce with partial = NULL, compare with the oracle"""
+        slot = step % 3
+        for p in range(world):
+            got = bufs_t[p].view(3, world, d)[slot, 0].cpu().view(torch.float16)
+            assert torch.equal(got, mine.reshape(-1)), f"piece of rank 0 in rank {p}'s buffer"
+        others = rand(gen, (world - 1, 1, d))
+        others[others == 0] = 0.0
+        for p in range(1, world):
+            own[slot, p] = others[p - 1].reshape(-1).view(torch.int16).to(cuda)
+        y = torch.empty(1, d, dtype=torch.float16, device=cuda)
+        r = torch.empty(1, d, dtype=torch.float16, device=cuda)
+        _lib.call("djv_allreduce_add_layernorm", comm, y.data_ptr(), r.data_ptr(), None, res.to(cuda).data_ptr(),
+                  gamma.data_ptr(), beta.data_ptr(), 1, d, 1e-5, st)
+        assert lib.djv_comm_status(comm) == 0
+        acc = mine.float().reshape(1, d).clone()
+        for p in range(world - 1):
+            acc += others[p].float()
+        y_ref, r_ref = O.add_layernorm(acc.half(), res, gamma.cpu(), beta.cpu(), 1e-5)
+        assert torch.equal(r.cpu(), r_ref)
+        close(y, y_ref, atol=2e-3)
+
+    # step 0: fc2 (gather transposed GEMV)
+    W2t, b2 = rand(gen, (Z, d), 0.05), rand(gen, (d,), 0.1)
+    h = rand(gen, (1, M))
+    idx = torch.randperm(Z, generator=gen)[:M].sort().values.int()
+    want = ops.gather_transposed_gemv(h.to(cuda), W2t.to(cuda), idx.to(cuda), b2.to(cuda)).cpu()
+    want[want == 0] = 0.0
+    need = lib.djv_gather_transposed_gemv_scratch_bytes(1, d, M)
+    scratch = torch.zeros(need, dtype=torch.uint8, device=cuda)
+    Wd, hd_, idxd, bd = W2t.to(cuda), h.to(cuda), idx.to(cuda), b2.to(cuda)
+    _lib.call("djv_gather_transposed_gemv_push", comm, Wd.data_ptr(), hd_.data_ptr(), idxd.data_ptr(), bd.data_ptr(),
+              1, d, M, d, 0, scratch.data_ptr(), need, st)
+    finish(0, want, rand(gen, (1, d)))
+
+    # step 1: out_proj over selected heads
+    Wo, bo = rand(gen, (d, nheads, hd), 0.05), rand(gen, (d,), 0.1)
+    ctx = rand(gen, (1, nheads, hd))
+    heads = torch.tensor([1, 3], dtype=torch.int32)
+    want = ops.out_proj_sparse(ctx.to(cuda), Wo.to(cuda), heads.to(cuda), bo.to(cuda)).cpu()
+    want[want == 0] = 0.0
+    Wod, ctxd, headsd, bod = Wo.to(cuda), ctx.to(cuda), heads.to(cuda), bo.to(cuda)
+    _lib.call("djv_out_proj_sparse_push", comm, Wod.data_ptr(), ctxd.data_ptr(), headsd.data_ptr(), None,
+              bod.data_ptr(), 1, d, nheads, hd, 2, st)
+    finish(1, want, rand(gen, (1, d)))
+    lib.djv_comm_destroy(comm)
