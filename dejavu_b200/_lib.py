@@ -63,6 +63,7 @@ SIGNATURES = {
     "djv_comm_create": (_i, [C.POINTER(_vp), _i, _i, C.POINTER(_vp), _sz]),
     "djv_gather_transposed_gemv_push": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _sz, _vp]),
     "djv_out_proj_sparse_push": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "djv_set_early_weight_prefetch": (None, [_i]),
     "djv_comm_destroy": (_i, [_vp]),
     "djv_comm_status": (_i, [_vp]),
     "djv_allreduce_add_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),

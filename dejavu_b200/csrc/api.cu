@@ -28,6 +28,9 @@ int check_launch(const char *what) {
   return DJV_OK;
 }
 
+static thread_local int g_early_prefetch = 0;
+bool early_prefetch() { return g_early_prefetch != 0 && pdl_enabled(); }
+
 bool pdl_enabled() {
   static const bool on = env_int("DJV_PDL", 1) != 0;
   return on;
@@ -49,6 +52,8 @@ int sm_count() {
 }  // namespace djv
 
 extern "C" int djv_version(void) { return 100; }
+
+extern "C" void djv_set_early_weight_prefetch(int enabled) { djv::g_early_prefetch = enabled; }
 
 extern "C" const char *djv_last_error(void) { return djv::g_err; }
 

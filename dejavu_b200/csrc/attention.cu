@@ -75,6 +75,7 @@ struct QkvArgs {
   // from x_cur, and block 0 copies it into the window for later back-fills. Null otherwise.
   const __half *x_cur;
   __half *x_ring_w;
+  int early;  // MODE 1: the state is complete before this kernel can start; prefetch weights before the wait
 };
 
 // ROWS weight rows against NB token rows: every activation chunk is loaded (through L1) once and used for
@@ -214,9 +215,28 @@ __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, i
 // warps takes ROWS of them. Every group sees the same token rows, so the block-wide barriers are uniform.
 template <int MODE, int WPR, int ROWS>
 __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
-  pdl_prologue();
   constexpr int GROUPS = QKV_WARPS / WPR;
   constexpr int RPB = GROUPS * ROWS;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (MODE == 1 && RPB >= 8 && a.early) {
+    // The step was opened by an earlier, completed kernel (the caller's promise): the head this block works on
+    // is known, so the first 4 KB of each of its weight rows are requested while the LayerNorm before this
+    // kernel is still running.
+    const int jblocks_pf = a.hd / RPB;
+    const int pair_pf = blockIdx.x / jblocks_pf, jb_pf = blockIdx.x % jblocks_pf;
+    const int i_pf = pair_pf / 3, qkv_pf = pair_pf % 3;
+    if (i_pf < a.state[ST_NEFF]) {
+      const int h_pf = st_eff(a.state, a.nheads)[i_pf];
+      const char *w0 = reinterpret_cast<const char *>(a.w + (((size_t)qkv_pf * a.nheads + h_pf) * a.hd + jb_pf * RPB) * a.d);
+      const size_t row_bytes = (size_t)a.d * 2;
+      constexpr int LINES = 32;  // 128-byte lines per row
+      for (int l = threadIdx.x; l < RPB * LINES; l += QKV_THREADS) {
+        const int row = l / LINES, line = l % LINES;
+        if ((size_t)line * 128 < row_bytes) prefetch_l2(w0 + row * row_bytes + (size_t)line * 128);
+      }
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int U = (ROWS == 1) ? 8 : (ROWS == 2 ? 4 : 2);  // ROWS * U = 8 weight loads in flight per lane
   __shared__ float red[QKV_WARPS][ROWS][8];
   __shared__ int rows_s[DJV_KV_WINDOW];
@@ -558,18 +578,34 @@ template <int HD, int B>
 __global__ void __launch_bounds__(OP_THREADS)
 out_proj_sparse_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                        const int *__restrict__ head_idx, const int *__restrict__ n_active_dev,
-                       const __half *__restrict__ bias, int d, int nheads, int nnz, PushTarget push) {
-  pdl_prologue();
+                       const __half *__restrict__ bias, int d, int nheads, int nnz, PushTarget push,
+                       int early) {
   constexpr int LPS = HD / 8;      // lanes per segment
   constexpr int SEGS = WARP / LPS; // segments per warp load
   const int tid = threadIdx.x, lane = tid % WARP;
   const int gw = (blockIdx.x * OP_THREADS + tid) / WARP;
   const int n0 = gw * OP_ROWS;
+  const int seg = lane / LPS, c = lane % LPS;
+  const size_t row_stride = (size_t)nheads * HD;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (early && n0 < d) {
+    // The head list is complete (the caller's promise): while the attention kernel before this one is still
+    // running, ask for every weight segment this warp is going to read. One lane per 128-byte line.
+    int n_pf = nnz;
+    if (n_active_dev) n_pf = min(nnz, *n_active_dev);
+    if (c % 8 == 0) {
+      for (int i = seg; i < n_pf; i += SEGS) {
+        const int h = head_idx[i];
+#pragma unroll
+        for (int r = 0; r < OP_ROWS; ++r)
+          if (n0 + r < d) prefetch_l2(W + (size_t)(n0 + r) * row_stride + (size_t)h * HD + c * 8);
+      }
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (n0 >= d) return;
   int n_eff = nnz;
   if (n_active_dev) n_eff = min(nnz, *n_active_dev);
-  const int seg = lane / LPS, c = lane % LPS;
-  const size_t row_stride = (size_t)nheads * HD;
 
   float acc[OP_ROWS][B];
 #pragma unroll
@@ -730,10 +766,11 @@ template <int HD>
 static int launch_out_proj(int B, __half *Y, const __half *W, const __half *X, const int *head_idx,
                            const int *n_active_dev, const __half *bias, int d, int nheads, int nnz,
                            cudaStream_t st, const PushTarget &push = PushTarget{}) {
+  const int early = early_prefetch() ? 1 : 0;
   const int warps = ceil_div(d, OP_ROWS);
   const int grid = ceil_div(warps * WARP, OP_THREADS);
 #define DJV_OP(B_) \
-  djv::launch_kernel(out_proj_sparse_kernel<HD, B_>, grid, OP_THREADS, 0, st, Y, W, X, head_idx, n_active_dev, bias, d, nheads, nnz, push)
+  djv::launch_kernel(out_proj_sparse_kernel<HD, B_>, grid, OP_THREADS, 0, st, Y, W, X, head_idx, n_active_dev, bias, d, nheads, nnz, push, early)
   switch (B) {
     case 1: DJV_OP(1); break;
     case 2: DJV_OP(2); break;
@@ -900,6 +937,7 @@ extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *
   if (step_is_open) {
     a.x_cur = static_cast<const __half *>(x);
     a.x_ring_w = static_cast<__half *>(x_ring);
+    a.early = early_prefetch() ? 1 : 0;
   }
   const int typical = head_idx ? (nnz > 0 ? nnz : 1) : nheads;
   launch_qkv<1>(a, nheads, (long long)typical * 3 * hd, st);

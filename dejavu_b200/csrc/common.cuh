@@ -38,6 +38,9 @@ inline int env_int(const char *name, int dflt) {
 // writes are visible, before it touches any memory. Only launch latency is overlapped; ordering of data is
 // the same as without PDL. DJV_PDL=0 in the environment launches the classic way.
 bool pdl_enabled();
+// Set by djv_set_early_weight_prefetch for the calling thread: kernels may read their index list / attention
+// state and prefetch weight rows into L2 before they wait for the kernel launched just before them.
+bool early_prefetch();
 
 template <typename... P, typename... A>
 inline cudaError_t launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
@@ -82,6 +85,11 @@ constexpr int WARP = 32;
 __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Hint: bring the 128-byte line at p into L2 (fire and forget).
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // 16-byte read-only load that does not pollute L1 (weights are streamed exactly once).

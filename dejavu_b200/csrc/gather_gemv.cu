@@ -29,8 +29,7 @@ template <int B, int ACT, int WPR, int ROWS, int U>
 __global__ void __launch_bounds__(RD_THREADS)
 rowdot_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
               const void *__restrict__ idx, const __half *__restrict__ bias, int M, int N,
-              long long ldw, int idx64) {
-  pdl_prologue();
+              long long ldw, int idx64, int early) {
   constexpr int GROUPS = RD_WARPS / WPR;
   constexpr int GLANES = WARP * WPR;
   __shared__ float red[WPR > 1 ? RD_WARPS * ROWS * B : 1];
@@ -41,6 +40,25 @@ rowdot_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half
   const int glane = wig * WARP + lane;
   const int nchunks = N / 8;
   const uint4 *Xv = reinterpret_cast<const uint4 *>(X);
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (early) {
+    // Weights are not produced by any kernel, and the index list is complete (identity, or the caller's
+    // promise): the first 8 KB of the first rows of this group are requested while the kernel before this
+    // one is still running.
+    const int m0 = blockIdx.x * GROUPS * ROWS + group * ROWS;
+    constexpr int LINES = 64;
+    const int row_lines = (int)min((long long)LINES, ((long long)N * 2 + 127) / 128);
+#pragma unroll
+    for (int j = 0; j < ROWS; ++j) {
+      if (m0 + j < M) {
+        const long long r = load_index(idx, m0 + j, idx64);
+        const char *w0 = reinterpret_cast<const char *>(W + r * ldw);
+        for (int l = glane; l < row_lines; l += GLANES) prefetch_l2(w0 + (size_t)l * 128);
+      }
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int rows_per_pass = gridDim.x * GROUPS * ROWS;
   // trip count is uniform over the block so that __syncthreads below is legal
@@ -167,7 +185,7 @@ static void launch_rowdot(const RowdotPlan &p, __half *Y, const __half *W, const
                           int idx64, cudaStream_t st) {
 #define DJV_RD(WPR_, ROWS_)                                                               \
   djv::launch_kernel(rowdot_kernel<B, ACT, WPR_, ROWS_, 4>, p.grid, RD_THREADS, 0, st, Y, W, X, idx, bias, M, N, \
-                                                                       ldw, idx64)
+                     ldw, idx64, (idx == nullptr || early_prefetch()) ? 1 : 0)
   constexpr int R = (B <= 2) ? 2 : 1;
   switch (p.wpr) {
     case 1: DJV_RD(1, R); break;

@@ -42,6 +42,8 @@ SIDE_STREAMS_ENABLED = os.environ.get("DJV_SIDE_STREAMS", "1") != "0"
 FUSE_STEP_OPEN = os.environ.get("DJV_FUSE_STEP_OPEN", "1") != "0"
 # fc2 and out_proj send their result into the peers' receive buffers themselves (development knob)
 PUSH_PARTIALS = os.environ.get("DJV_PUSH_PARTIALS", "1") != "0"
+# kernels whose index list is known to be complete prefetch weights before their PDL wait (development knob)
+EARLY_PREFETCH = os.environ.get("DJV_EARLY_PREFETCH", "1") != "0"
 _SIDE_STREAMS: dict = {}
 _SIDE_DIRTY: dict = {}  # device index -> names of side streams forked since the last join
 
@@ -96,7 +98,12 @@ def _wait_ready(t):
     """Make the current stream wait for a tensor produced on a side stream (no-op otherwise)."""
     ev = None if t is None else getattr(t, "_ready_event", None)
     if ev is not None:
-        torch.cuda.current_stream().wait_event(ev)
+        stream = torch.cuda.current_stream()
+        # once per stream: a second wait would add a second edge to the next kernel of a captured graph, and a
+        # kernel with two incoming edges is not launched programmatically any more
+        if getattr(t, "_waited_on", None) != stream.cuda_stream:
+            stream.wait_event(ev)
+            t._waited_on = stream.cuda_stream
 
 
 def join_side_streams(device):
@@ -265,8 +272,10 @@ class ParallelFusedMLPDejavu(nn.Module):
         if idx is not None:
             assert x.size(1) == 1
             assert self.activation == "relu", "the sparse path applies ReLU (gather_gemv.py:655)"
-            out = ops.mlp_sparse(x.view(x.size(0), -1), self.fc1.weight, self.fc2.weight_t, idx, self.fc1.bias,
-                                 self.fc2.bias, push_comm=self.push_comm)
+            # idx came from a side stream and the main stream has waited on its event already
+            with ops.indices_ready(EARLY_PREFETCH and getattr(idx, "_ready_event", None) is not None):
+                out = ops.mlp_sparse(x.view(x.size(0), -1), self.fc1.weight, self.fc2.weight_t, idx, self.fc1.bias,
+                                     self.fc2.bias, push_comm=self.push_comm)
             out = out.view(x.size(0), 1, -1)
         elif do_token_generation and not self.dense_decode_cublas:
             act = "relu" if self.activation == "relu" else "gelu_approx"
@@ -410,10 +419,13 @@ class ParallelMHASparseAttMlp(nn.Module):
         bias = self.Wqkv.bias
         # the layer before may have opened this step already, in the kernel that selected the heads
         step_is_open = 1 if (head_idx is not None and getattr(head_idx, "_step_opened_for", None) is self) else 0
-        call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
-             None if bias is None else bias.data_ptr(), xf.data_ptr(), b["x_ring"].data_ptr(), k_cache.data_ptr(),
-             v_cache.data_ptr(), b["state"].data_ptr(), None if head_idx is None else head_idx.data_ptr(), nnz, d, n,
-             hd, S, step_is_open, st)
+        # an opened step means the state was written on a side stream whose event the main stream has waited on
+        early = EARLY_PREFETCH and step_is_open == 1 and getattr(head_idx, "_ready_event", None) is not None
+        with ops.indices_ready(early):
+            call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
+                 None if bias is None else bias.data_ptr(), xf.data_ptr(), b["x_ring"].data_ptr(), k_cache.data_ptr(),
+                 v_cache.data_ptr(), b["state"].data_ptr(), None if head_idx is None else head_idx.data_ptr(), nnz, d,
+                 n, hd, S, step_is_open, st)
         if between is not None:
             between()
         call("djv_attn_step_attend", b["ctx"].data_ptr(), b["q"].data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
@@ -424,14 +436,15 @@ class ParallelMHASparseAttMlp(nn.Module):
         state = b["state"]
         eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
         n_eff_ptr = state.data_ptr() + 4 * 2
-        if self.push_comm is not None:
-            call("djv_out_proj_sparse_push", self.push_comm.handle, self.out_proj.weight.data_ptr(),
-                 b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd,
-                 n, st)
-            self.push_comm.note_pushed(out)
-        else:
-            call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
-                 eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
+        with ops.indices_ready(early):
+            if self.push_comm is not None:
+                call("djv_out_proj_sparse_push", self.push_comm.handle, self.out_proj.weight.data_ptr(),
+                     b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n,
+                     hd, n, st)
+                self.push_comm.note_pushed(out)
+            else:
+                call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
+                     eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
         # the window advance is folded into the next step's first kernel (no djv_attn_step_finish launch)
         return out.view(1, 1, d)
 
@@ -552,6 +565,9 @@ class BlockMlpAttSparse(nn.Module):
 
     def forward(self, hidden_states, residual=None, mixer_subset=None, mixer_kwargs=None, head_idx=None,
                 mlp_sp_logit=None, hidden_is_partial=False):
+        # the wait for the head list goes before the LayerNorm launch, so that the QKV projection follows the
+        # LayerNorm with a single (programmatic) edge and can prefetch its weights while the LayerNorm runs
+        _wait_ready(head_idx)
         hidden_states, residual = self._add_norm(hidden_states, residual, self.norm1, hidden_is_partial)
         if mixer_kwargs is None:
             mixer_kwargs = {}

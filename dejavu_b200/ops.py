@@ -9,6 +9,8 @@ There is no CPU path: tensors must live on a CUDA device.
 """
 from __future__ import annotations
 
+import contextlib
+
 from typing import Optional
 
 import torch
@@ -298,6 +300,22 @@ def topk_indices(scores: torch.Tensor, k: int, dtype: torch.dtype = torch.int64)
     a32, a64 = (out.data_ptr(), None) if dtype == torch.int32 else (None, out.data_ptr())
     call("djv_topk", a32, a64, scores.data_ptr(), n, k, 1 if scores.dtype == torch.float32 else 0, _stream())
     return out
+
+
+@contextlib.contextmanager
+def indices_ready(ready: bool = True):
+    """Inside this block the caller promises that the index lists / attention state passed to the operators
+    are complete before the kernels can start (produced on another stream and joined with an event): the
+    kernels then prefetch their weight rows while the kernel launched before them is still running
+    (see djv_set_early_weight_prefetch)."""
+    lib = _lib.load()
+    if ready:
+        lib.djv_set_early_weight_prefetch(1)
+    try:
+        yield
+    finally:
+        if ready:
+            lib.djv_set_early_weight_prefetch(0)
 
 
 def topk_indices_open_step(scores: torch.Tensor, k: int, state: torch.Tensor, cache_len: int) -> torch.Tensor:

@@ -47,6 +47,14 @@ const char *djv_last_error(void);
 const char *djv_status_string(int status);
 /* Number of kernels launched by this library on this process since load (all threads). */
 unsigned long long djv_launch_count(void);
+/* Per calling thread, default 0. While set, the gather / head-sparse kernels launched by this thread read
+ * their index list (idx, head_idx, the attention state) and prefetch the first weight rows into L2 BEFORE
+ * they wait for the kernel launched just before them on the stream (they are launched with programmatic
+ * dependent launch and would otherwise idle until it has drained). The caller thereby promises that those
+ * index arguments are complete before the launch can start: produced on another stream and joined with an
+ * event, or by earlier work ordered by a full (non-programmatic) dependency. Activations are still read
+ * after the wait. Kernels without an index list (idx == NULL) always prefetch. No reference counterpart. */
+void djv_set_early_weight_prefetch(int enabled);
 
 /* ---------------------------------------------------------------------------------------------
  * Gather GEMV (fc1):  y[b,m] = act( sum_n w[idx[m],n] * x[b,n] + bias[idx[m]] ),  b<B, m<M.
