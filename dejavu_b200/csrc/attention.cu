@@ -291,8 +291,8 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
     __shared__ float red_mma[QKV_WARPS * 2 * 16 * 8];
     if (nrows <= 8) qkv_mma_rows<MODE, RPB, 1>(a, qkv, h, jb * RPB, nrows, rows_s, base, slot, red_mma);
     else qkv_mma_rows<MODE, RPB, 2>(a, qkv, h, jb * RPB, nrows, rows_s, base, slot, red_mma);
-    return;
-  }
+    // (the CUDA-core path below is compiled for the one-row-per-block variant only)
+  } else {
 
   const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
   const int group = warp / WPR, wig = warp % WPR, glane = wig * WARP + lane;
@@ -390,6 +390,7 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
     }
     if (WPR > 1) __syncthreads();
   }
+  }  // RPB < 8
 }
 
 // ------------------------------------------------------------------------------------------
