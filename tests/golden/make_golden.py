@@ -168,7 +168,7 @@ def block_case(ref_root: Path):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of FMInference/DejaVu to import and run")
     a = ap.parse_args()
     root = Path(a.reference)
     blk = block_case(root)

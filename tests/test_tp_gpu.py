@@ -69,10 +69,11 @@ def _decode_run(model, cfg, ids, steps, dev, pg, rank, world, record):
 
 
 def _log(rank, msg):
-    """Progress marker (helps to see where a multi-rank run stopped)."""
-    d = ROOT / "gpurun_out"
-    if d.is_dir():
-        with open(d / f"tp_progress_rank{rank}.log", "a") as f:
+    """Progress marker (helps to see where a multi-rank run stopped): appended to
+    $DJV_TEST_LOG_DIR/tp_progress_rank<r>.log when that variable names a directory."""
+    d = os.environ.get("DJV_TEST_LOG_DIR")
+    if d and os.path.isdir(d):
+        with open(os.path.join(d, f"tp_progress_rank{rank}.log"), "a") as f:
             f.write(msg + "\n")
 
 
