@@ -101,6 +101,13 @@ __device__ __forceinline__ uint4 ld_stream16(const void *p) {
   return v;
 }
 
+// Pins a loaded value at this point of the instruction stream: placed after a group of ld_stream16 calls (all
+// of them volatile asm, hence kept in order), it keeps the compiler from sinking the later loads of the group
+// below arithmetic on the earlier ones, i.e. all loads of the group are in flight before any is consumed.
+__device__ __forceinline__ void keep_loaded(uint4 &v) {
+  asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w));
+}
+
 // 16-byte cached load (activations, small reused vectors).
 __device__ __forceinline__ uint4 ld_cached16(const void *p) {
   return __ldg(reinterpret_cast<const uint4 *>(p));
