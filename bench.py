@@ -190,7 +190,8 @@ def run_reference(args, cfg, mlp_K, att_K, world, rank):
     from oracle import cpu_bench
 
     r = cpu_bench.time_decode(cfg.hidden_size, cfg.n_head, cfg.n_inner, cfg.n_layer, cfg.vocab_size, mlp_K, att_K,
-                              S=256, sample_layers=1, reps=max(2, min(args.steps, 4)))
+                              S=256, sample_layers=2, reps=max(2, min(args.steps, 4)),
+                              threads=cpu_bench.host_threads())
     line = base_line(args, cfg, mlp_K, att_K, world)
     line.update({
         "impl": "reference", "value": round(r["ms_per_token"], 3), "ms_per_step": round(r["ms_per_token"], 3),
@@ -406,7 +407,8 @@ def main():
         from oracle import cpu_bench
 
         r = cpu_bench.time_decode(cfg.hidden_size, cfg.n_head, cfg.n_inner, cfg.n_layer, cfg.vocab_size,
-                                  mlp_K if cfg.mlp_sparse else None, att_K1 if cfg.att_sparse else None)
+                                  mlp_K if cfg.mlp_sparse else None, att_K1 if cfg.att_sparse else None,
+                                  threads=cpu_bench.host_threads())
         line["cpu_baseline"] = {"value": round(r["ms_per_token"], 2), "unit": "ms/token", "cores": r["cores"],
                                 "kind": "port", "sample": r["sample"]}
     if rank == 0:

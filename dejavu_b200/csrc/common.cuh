@@ -113,13 +113,6 @@ __device__ __forceinline__ uint4 ld_cached16(const void *p) {
   return __ldg(reinterpret_cast<const uint4 *>(p));
 }
 
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
-  unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
 __device__ __forceinline__ float2 h2f(uint32_t u) {
   __half2 h = *reinterpret_cast<__half2 *>(&u);
   return __half22float2(h);

@@ -155,14 +155,11 @@ static RowdotPlan plan_rowdot(int M, int N, int B) {
   const int sms = sm_count();
   const int nchunks = N / 8;
   const int rows = (B <= 2) ? 2 : 1;
-  // enough warps for ~32 resident warps per SM, but at least one chunk per lane
-  static const int k_warps = env_int("DJV_RD_WARPS_PER_SM", 32);   // development knobs
-  static const int k_wpr = env_int("DJV_RD_WPR", 0);
+  static const int k_wpr = env_int("DJV_RD_WPR", 0);  // development knobs
   static const int k_cap = env_int("DJV_RD_BLOCKS_PER_SM", 6);
   // As many warps per row as still lets every block be resident at once (4 blocks of 256 threads per SM):
   // a second, partial wave of blocks costs more than fewer lanes per row (measured: K=4096, d=9216 runs at
   // 0.77 of the HBM peak with 2 warps per row, 0.71 with 4, 0.67 with 1).
-  (void)k_warps;
   const long long resident = (long long)sms * 4;
   int wpr = 1;
   while (wpr < 8 && (long long)ceil_div(M, (RD_WARPS / (wpr * 2)) * rows) <= resident && nchunks >= 64 * wpr * 2)

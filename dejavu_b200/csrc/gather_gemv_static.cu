@@ -67,6 +67,9 @@ extern "C" int djv_gather_transposed_gemv_static(void *y, const void *w, const v
   DJV_REQUIRE(M >= 1, "gather_transposed_gemv_static: M=%d must be at least 1", M);
   DJV_REQUIRE(ldw >= N && ldw % 8 == 0, "gather_transposed_gemv_static: bad row stride %lld", ldw);
   DJV_REQUIRE(aligned16(w), "gather_transposed_gemv_static: weight pointer must be 16-byte aligned");
+  // the finishing stage stores 16 bytes at a time to y and loads 16 bytes at a time from bias
+  DJV_REQUIRE(aligned16(y), "gather_transposed_gemv_static: y must be 16-byte aligned");
+  DJV_REQUIRE(bias == nullptr || aligned16(bias), "gather_transposed_gemv_static: bias must be 16-byte aligned");
   const size_t need = rowaxpy_scratch_bytes(B, N, M);
   if (need > DJV_STATIC_SCRATCH_BYTES) {
     set_error("gather_transposed_gemv_static: B=%d N=%d M=%d needs %zu bytes of scratch, the built-in array holds "

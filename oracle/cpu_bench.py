@@ -22,7 +22,8 @@ from . import oracle as O
 
 
 def _rand(*shape):
-    return torch.empty(*shape, dtype=torch.float32).uniform_(-0.03, 0.03)
+    """N(0, 0.02), the synthetic weight distribution of every benchmark configuration."""
+    return torch.empty(*shape, dtype=torch.float32).normal_(0.0, 0.02)
 
 
 class CpuLayer:
@@ -67,12 +68,24 @@ class CpuLayer:
         return h, residual, next_logit, next_att
 
 
-def time_decode(d, H, ffn, n_layer, vocab, mlp_K, att_K, S=256, sample_layers=1, reps=3, R_mlp=1000, R_att=1000,
+def host_threads() -> int:
+    """Host threads this process may use (launchers such as torch.distributed.run export OMP_NUM_THREADS=1,
+    which would otherwise leave the CPU arm on a single core)."""
+    import os
+
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def time_decode(d, H, ffn, n_layer, vocab, mlp_K, att_K, S=256, sample_layers=2, reps=3, R_mlp=1000, R_att=1000,
                 threads=None):
-    """Returns dict(ms_per_token, ms_per_layer, ms_lm_head, cores, sample). mlp_K / att_K None = dense."""
-    if threads:
-        torch.set_num_threads(threads)
+    """Returns dict(ms_per_token, ms_per_layer, ms_lm_head, cores, sample). mlp_K / att_K None = dense.
+    threads: host threads to use (default: every core this process may run on)."""
+    torch.set_num_threads(threads or host_threads())
     cores = torch.get_num_threads()
+    sample_layers = max(1, min(sample_layers, n_layer))
     layers = [CpuLayer(d, H, ffn, R_mlp, R_att, S) for _ in range(sample_layers)]
     W_lm = _rand(vocab, d) if vocab else None
     h, residual = torch.randn(1, d), torch.randn(1, d)

@@ -69,6 +69,22 @@ def test_argument_validation_happens_before_any_launch(lib):
     assert lib.djv_launch_count() == before
 
 
+def test_static_scratch_entry_point_checks_alignment_on_the_host(lib):
+    """The allocation-free fc2 entry point validates like the regular one: a y or bias pointer that is not
+    16-byte aligned is refused before anything is launched (the kernel stores and loads 16 bytes at a time)."""
+    from dejavu_b200 import _lib
+
+    before = lib.djv_launch_count()
+    ok, odd = ctypes.c_void_p(0x1000), ctypes.c_void_p(0x1002)
+    rc = lib.djv_gather_transposed_gemv_static(odd, ok, ok, ok, None, 1, 128, 4, 128, 0, None)
+    assert rc == _lib.ERR_INVALID and b"y must be 16-byte aligned" in lib.djv_last_error()
+    rc = lib.djv_gather_transposed_gemv_static(ok, ok, ok, ok, odd, 1, 128, 4, 128, 0, None)
+    assert rc == _lib.ERR_INVALID and b"bias must be 16-byte aligned" in lib.djv_last_error()
+    rc = lib.djv_gather_transposed_gemv_static(ok, odd, ok, ok, None, 1, 128, 4, 128, 0, None)
+    assert rc == _lib.ERR_INVALID
+    assert lib.djv_launch_count() == before
+
+
 def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     from dejavu_b200 import _lib
 

@@ -57,6 +57,26 @@ def test_static_scratch_entry_point_matches_regular_one_twice(cuda, Z, N, M, B):
         assert torch.equal(got, want), f"call {call_no}: expected identical bits"
 
 
+@pytest.mark.parametrize("Z,M,B,widths", [(8192, 4096, 1, (1024, 2048)), (8192, 4096, 4, (2048, 1024))])
+def test_static_scratch_array_is_really_used_and_reused(cuda, Z, M, B, widths):
+    """Shapes whose plan splits the index list over several clusters per column tile: the kernel then keeps
+    per-cluster partial sums and arrival counters in the built-in array. Two calls in a row with DIFFERENT
+    output widths, so the second one finds the first one's partial sums and counters in the array."""
+    from dejavu_b200 import _lib
+
+    lib = _lib.load()
+    for call_no, N in enumerate(widths):
+        need = lib.djv_gather_transposed_gemv_scratch_bytes(B, N, M)
+        if need <= 4096 + B * N * 4:
+            pytest.skip("the plan keeps one cluster per column tile on this device: no partial sums in scratch")
+        assert need <= STATIC_SCRATCH_BYTES
+        W, h, bias, idx = _inputs(cuda, 31 + call_no, Z, N, M, B)
+        want = _regular(_lib, W, h, bias, idx, B, N, M)
+        got = _static(_lib, W, h, bias, idx, B, N, M)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"call {call_no} (N={N}): expected identical bits"
+
+
 def test_static_scratch_entry_point_refuses_oversized_requests(cuda):
     from dejavu_b200 import _lib
 
