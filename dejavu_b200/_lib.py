@@ -15,6 +15,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_SCRATCH, ERR_TIMEOUT = 0, -1, -2
 ACT = {"id": 0, "relu": 1, "gelu": 2, "gelu_approx": 3, "squared_relu": 4}
 MAX_BATCH = 32
 KV_WINDOW = 16
+EXCHANGE_REFILL = 1
 ATTN_STATE_HDR = 8
 
 
@@ -61,12 +62,19 @@ SIGNATURES = {
     "djv_ipc_close": (_i, [_vp]),
     "djv_comm_buffer_bytes": (_sz, [_i, _sz]),
     "djv_comm_create": (_i, [C.POINTER(_vp), _i, _i, C.POINTER(_vp), _sz]),
-    "djv_gather_transposed_gemv_push": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _sz, _vp]),
-    "djv_out_proj_sparse_push": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "djv_gather_transposed_gemv_push": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _sz, _vp]),
+    "djv_out_proj_sparse_push": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "djv_comm_end_step": (_i, [_vp, _i, _vp]),
+    "djv_mlp_sparse_fused_supported": (_i, [_i, _i, _i]),
+    "djv_mlp_sparse_fused_scratch_bytes": (_sz, [_i, _i, _i]),
+    "djv_mlp_ring_timeouts": (C.c_uint, []),
+    "djv_mlp_sparse_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
+    "djv_mlp_sparse_fused_exchange": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp,
+                                           _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
     "djv_set_early_weight_prefetch": (None, [_i]),
     "djv_comm_destroy": (_i, [_vp]),
     "djv_comm_status": (_i, [_vp]),
-    "djv_allreduce_add_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "djv_allreduce_add_layernorm": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
 }
 
 _lib = None

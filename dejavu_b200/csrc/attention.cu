@@ -809,12 +809,13 @@ extern "C" int djv_out_proj_sparse(void *y, const void *w, const void *x, const 
 }
 
 // The same projection with the result sent into every rank's receive buffer of the tensor-parallel exchange
-// instead of y (see push.cuh): the NVLink trip overlaps the kernel's tail, and the all-reduce kernel that
-// follows is called with partial == NULL.
-extern "C" int djv_out_proj_sparse_push(djv_comm *comm, const void *w, const void *x, const int32_t *head_idx,
+// instead of y, as exchange number `seq` of the step (see push.cuh): the NVLink trip overlaps the kernel's
+// tail, and the consumer of that exchange is called with partial == NULL.
+extern "C" int djv_out_proj_sparse_push(djv_comm *comm, int seq, const void *w, const void *x, const int32_t *head_idx,
                                         const int32_t *n_active_dev, const void *bias, int B, int d,
                                         int nheads, int hd, int nnz, void *stream) {
   DJV_REQUIRE(comm && w && x && (head_idx || nnz == 0), "out_proj_sparse_push: null pointer");
+  DJV_REQUIRE(seq >= 0, "out_proj_sparse_push: negative exchange number %d", seq);
   int rc = check_hd("out_proj_sparse_push", hd, d);
   if (rc) return rc;
   DJV_REQUIRE(B >= 1 && B <= 4, "out_proj_sparse_push: batch %d outside [1,4]", B);
@@ -825,7 +826,7 @@ extern "C" int djv_out_proj_sparse_push(djv_comm *comm, const void *w, const voi
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __half *W = static_cast<const __half *>(w), *X = static_cast<const __half *>(x);
   const __half *bi = static_cast<const __half *>(bias);
-  const PushTarget push = push_target(comm);
+  const PushTarget push = push_target(comm, seq);
   if (hd == 128) rc = launch_out_proj<128>(B, nullptr, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st, push);
   else if (hd == 64) rc = launch_out_proj<64>(B, nullptr, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st, push);
   else rc = launch_out_proj<32>(B, nullptr, W, X, head_idx, n_active_dev, bi, d, nheads, nnz, st, push);

@@ -1,33 +1,16 @@
-// Tensor-parallel one-shot all-reduce fused with the residual add and LayerNorm that follow it.
+// Tensor-parallel one-shot all-reduce fused with the residual add and LayerNorm that follow it, as a kernel
+// of its own (the fused sparse-MLP kernel runs the same receiving code in its prologue, see exchange.cuh), and
+// the set-up / tear-down of the exchange.
 //
-// Push protocol, the data is its own arrival flag: every rank owns a receive buffer of
-// 3 slots x world pieces, mapped into every peer with CUDA IPC and filled with a sentinel (fp16 -0.0,
-// bits 0x8000). One call = one block per rank, step e uses slot e % 3:
-//   1. each thread stores its 16-byte chunks of this rank's partial into piece [rank] of slot e%3 of EVERY
-//      rank (plain stores over NVLink; -0.0 in the data is sent as +0.0, which changes no sum);
-//   2. each thread refills slot (e+2)%3 of the LOCAL buffer with the sentinel. That slot held step e-1,
-//      which this rank finished reading before it started step e, and no peer writes it again before step
-//      e+2, which a peer can only reach after this rank's step e+1 push, i.e. after this kernel ended;
-//   3. each thread polls (bounded) the same chunks of all pieces of the LOCAL slot e%3 until no half of a
-//      chunk is the sentinel, adds them in rank order in fp32 (same order on all ranks, so all ranks hold
-//      bit-identical results), rounds to fp16, adds the residual, and the block normalises.
-// One NVLink one-way trip per step, no fences, no remote loads. A 16-byte store may arrive in pieces: every
-// half of a chunk is checked, so a partly arrived chunk just keeps the thread polling.
-// The epoch lives in device memory and is advanced by the kernel, so a captured CUDA graph replays correctly.
-// No multicast / multimem objects are used: a peer that exits between steps cannot fault the others,
-// their next call just runs out its wait and reports DJV_ERR_TIMEOUT in the status word.
-#include "norm.cuh"
-#include "push.cuh"
+// One thread-block cluster of 8 blocks per row: each block owns an eighth of the row's 16-byte chunks, one
+// chunk per thread for hidden sizes up to 16384, so all pieces of the whole row are requested in one round of
+// loads; the LayerNorm statistics are merged over the cluster through distributed shared memory.
+#include "exchange.cuh"
 
 namespace djv {
 
-constexpr unsigned long long AR_WAIT_LIMIT_NS = 2000ull * 1000 * 1000;  // a wait on a peer gives up after 2 s
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
+constexpr int EX_THREADS = 256;
+constexpr int EX_CLUSTER = 8;
 
 __global__ void fill_sentinel_kernel(uint4 *p, size_t n16) {
   const uint4 s = make_uint4(AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2);
@@ -35,125 +18,34 @@ __global__ void fill_sentinel_kernel(uint4 *p, size_t n16) {
     p[i] = s;
 }
 
-template <int NCH>
-__global__ void __launch_bounds__(LN_THREADS)
-allreduce_add_layernorm_kernel(void *const *__restrict__ bufs, unsigned *__restrict__ epoch_status, int rank,
-                               int world, size_t slot_bytes, __half *__restrict__ y, __half *r_out,
-                               const __half *__restrict__ partial, const __half *residual,
-                               const __half *__restrict__ gamma, const __half *__restrict__ beta,
-                               int B, int d, float eps) {
-  __shared__ float red[LN_THREADS / WARP];
-  __shared__ int failed;
-  const int tid = threadIdx.x;
-  const int nchunks = d / 8;
+// ctl[0] += n: the exchanges of the step that just ended. Launched once per step, after every kernel of the
+// step that reads ctl[0] (all streams joined), so the value is stable while a step runs.
+__global__ void comm_end_step_kernel(unsigned *ctl, unsigned n) {
+  pdl_prologue();
+  if (threadIdx.x == 0) ctl[0] += n;
+}
+
+template <int ITEMS>
+__global__ void __cluster_dims__(EX_CLUSTER, 1, 1) __launch_bounds__(EX_THREADS)
+exchange_layernorm_kernel(FoldArgs a) {
+  __shared__ float red[EX_THREADS / WARP];
+  __shared__ float st[4], stf[2];
+  __shared__ int failed_s;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (int)cluster.block_rank();
+  const int row = blockIdx.y;
+  const int nchunks = a.d / 8;
+  const int per = (nchunks + EX_CLUSTER - 1) / EX_CLUSTER;
+  const int c_lo = min(nchunks, crank * per), c_hi = min(nchunks, c_lo + per);
   // the affine weights are fetched while the predecessor kernel may still be running
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  LnAffine<NCH> w;
-  ln_fetch_affine(w, gamma, beta, nchunks);
+  FoldRegs<ITEMS> fr;
+  fold_fetch_affine<EX_THREADS, ITEMS>(fr, a, c_lo, c_hi, row, 1);
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const unsigned epoch = epoch_status[0];
-  const int total_chunks = B * nchunks;
-  if (tid == 0) failed = 0;
-  // once a wait has run out the exchange is dead: later calls return at once instead of waiting again
-  if (epoch_status[1] != 0u) return;
-  __syncthreads();
-  const size_t cur_off = (size_t)(epoch % AR_SLOTS) * world * slot_bytes;
-  const size_t old_off = (size_t)((epoch + 2) % AR_SLOTS) * world * slot_bytes;
-
-  // 1. push this rank's partial into piece [rank] of the current slot of every rank
-  //    (partial == nullptr: the kernel that produced it has pushed it already, see push.cuh)
-  if (partial != nullptr) {
-    void *dst[AR_MAX_WORLD];
-#pragma unroll
-    for (int p = 0; p < AR_MAX_WORLD; ++p)
-      dst[p] = (p < world) ? static_cast<char *>(bufs[p]) + cur_off + (size_t)rank * slot_bytes : nullptr;
-    const uint4 *src = reinterpret_cast<const uint4 *>(partial);
-    for (int c = tid; c < total_chunks; c += LN_THREADS) {
-      uint4 v = src[c];
-      v.x = no_sentinel2(v.x); v.y = no_sentinel2(v.y); v.z = no_sentinel2(v.z); v.w = no_sentinel2(v.w);
-#pragma unroll
-      for (int p = 0; p < AR_MAX_WORLD; ++p)
-        if (p < world) st_sys16(static_cast<uint4 *>(dst[p]) + c, v);
-    }
-  }
-  // 2. the slot of the previous step becomes free again
-  char *local = static_cast<char *>(bufs[rank]);
-  {
-    const uint4 s = make_uint4(AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2);
-    for (int p = 0; p < world; ++p) {
-      uint4 *old_piece = reinterpret_cast<uint4 *>(local + old_off + (size_t)p * slot_bytes);
-      for (int c = tid; c < total_chunks; c += LN_THREADS) old_piece[c] = s;
-    }
-  }
-
-  // 3. wait for the same chunks of every piece, reduce in rank order, residual add, LayerNorm
-  const unsigned long long t_start = global_timer_ns();
-  bool gave_up = false;
-  for (int row = 0; row < B; ++row) {
-    const size_t off = (size_t)row * d;
-    float vals[NCH][8];
-    // the residual row is requested before the wait on the peers, not after it
-    uint4 rres[NCH];
-#pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-      const int ch = c * LN_THREADS + tid;
-      rres[c] = (residual && ch < nchunks) ? *reinterpret_cast<const uint4 *>(residual + off + (size_t)ch * 8)
-                                           : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-      const int ch = c * LN_THREADS + tid;
-      if (ch < nchunks && !gave_up) {
-        const char *piece0 = local + cur_off + (off + (size_t)ch * 8) * 2;
-        uint4 v[AR_MAX_WORLD];
-        unsigned missing = (1u << world) - 1u;
-        // all pieces are requested together; only the ones not there yet are asked for again
-        while (missing != 0u) {
-#pragma unroll
-          for (int p = 0; p < AR_MAX_WORLD; ++p)
-            if (missing >> p & 1u) v[p] = ld_sys16(piece0 + (size_t)p * slot_bytes);
-#pragma unroll
-          for (int p = 0; p < AR_MAX_WORLD; ++p)
-            if ((missing >> p & 1u) && arrived16(v[p])) missing &= ~(1u << p);
-          if (missing != 0u && global_timer_ns() - t_start > AR_WAIT_LIMIT_NS) {
-            gave_up = true;
-            break;
-          }
-        }
-        float f[8], t[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = 0.f;
-#pragma unroll
-        for (int p = 0; p < AR_MAX_WORLD; ++p) {  // rank order
-          if (p < world && !gave_up) {
-            unpack8(v[p], t);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] += t[e];
-          }
-        }
-        round_store8(f, nullptr);  // the all-reduced activation is an fp16 tensor
-        if (residual) {
-          unpack8(rres[c], t);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] += t[e];
-        }
-        if (!gave_up) round_store8(f, r_out ? r_out + off + (size_t)ch * 8 : nullptr);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) vals[c][e] = f[e];
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) vals[c][e] = 0.f;
-      }
-    }
-    if (gave_up) failed = 1;
-    __syncthreads();
-    if (failed) break;  // block-uniform
-    layernorm_store(vals, nchunks, d, w, eps, y + off, red);
-  }
-  if (tid == 0) {
-    if (failed) epoch_status[1] = (unsigned)DJV_ERR_TIMEOUT;
-    epoch_status[0] = epoch + 1;
-  }
+  exchange_fold<EX_THREADS, ITEMS>(a, cluster, EX_CLUSTER, c_lo, c_hi, row, 1, true, nullptr,
+                                   row * EX_CLUSTER + crank, (int)gridDim.y * EX_CLUSTER, fr, red, st, stf,
+                                   &failed_s);
+  cluster.sync();  // no block leaves while a peer may still read its statistics
 }
 
 }  // namespace djv
@@ -236,10 +128,12 @@ extern "C" int djv_comm_create(djv_comm **out, int rank, int world, void *const 
   djv_comm *c = new djv_comm();
   c->rank = rank; c->world = world; c->slot_bytes = slot_bytes;
   c->last_stream = nullptr;
+  c->bufs_dev = nullptr;
+  c->ctl_dev = nullptr;
   cudaError_t e = cudaMalloc(&c->bufs_dev, sizeof(void *) * AR_MAX_WORLD);
-  if (e == cudaSuccess) e = cudaMalloc(&c->epoch_dev, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMalloc(&c->ctl_dev, 2 * sizeof(unsigned));
   if (e == cudaSuccess) e = cudaMemcpy(c->bufs_dev, bufs, sizeof(void *) * world, cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = cudaMemset(c->epoch_dev, 0, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(c->ctl_dev, 0, 2 * sizeof(unsigned));
   if (e == cudaSuccess) {
     fill_sentinel_kernel<<<64, 256>>>(static_cast<uint4 *>(bufs[rank]), djv_comm_buffer_bytes(world, slot_bytes) / 16);
     e = cudaGetLastError();
@@ -257,7 +151,7 @@ extern "C" int djv_comm_create(djv_comm **out, int rank, int world, void *const 
 extern "C" int djv_comm_destroy(djv_comm *c) {
   if (!c) return DJV_OK;
   if (c->bufs_dev) cudaFree(c->bufs_dev);
-  if (c->epoch_dev) cudaFree(c->epoch_dev);
+  if (c->ctl_dev) cudaFree(c->ctl_dev);
   delete c;
   return DJV_OK;
 }
@@ -266,35 +160,57 @@ extern "C" int djv_comm_status(djv_comm *c) {
   DJV_REQUIRE(c, "comm_status: null comm");
   unsigned es[2] = {0, 0};
   cudaError_t e = cudaStreamSynchronize(c->last_stream);
-  if (e == cudaSuccess) e = cudaMemcpy(es, c->epoch_dev, sizeof(es), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemcpy(es, c->ctl_dev, sizeof(es), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) {
     set_error("comm_status: %s", cudaGetErrorString(e));
     return DJV_ERR_CUDA;
   }
-  if ((int)es[1] != 0) set_error("all-reduce: a peer did not arrive within the wait limit (epoch %u)", es[0]);
+  if ((int)es[1] != 0) set_error("exchange: a peer did not arrive within the wait limit (after %u exchanges of earlier steps)", es[0]);
   return (int)es[1];
 }
 
-extern "C" int djv_allreduce_add_layernorm(djv_comm *c, void *y, void *r_out, const void *partial,
-                                           const void *residual, const void *gamma, const void *beta,
-                                           int B, int d, float eps, void *stream) {
-  DJV_REQUIRE(c && y && gamma && beta, "allreduce_add_layernorm: null pointer");
-  DJV_REQUIRE(B >= 1 && d >= 8 && d % 8 == 0 && d / 8 <= LN_THREADS * LN_MAX_CHUNKS,
+extern "C" int djv_comm_end_step(djv_comm *c, int n_exchanges, void *stream) {
+  DJV_REQUIRE(c && n_exchanges >= 0, "comm_end_step: bad argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  c->last_stream = st;
+  if (n_exchanges == 0) return DJV_OK;
+  djv::launch_kernel(comm_end_step_kernel, 1, 32, 0, st, c->ctl_dev, (unsigned)n_exchanges);
+  count_launch();
+  return check_launch("comm_end_step");
+}
+
+extern "C" int djv_allreduce_add_layernorm(djv_comm *c, int seq, int flags, void *y, void *r_out,
+                                           const void *partial, const void *residual, const void *gamma,
+                                           const void *beta, int B, int d, float eps, void *stream) {
+  DJV_REQUIRE(c != nullptr, "allreduce_add_layernorm: null comm");
+  DJV_REQUIRE((gamma == nullptr) == (beta == nullptr), "allreduce_add_layernorm: gamma and beta go together");
+  DJV_REQUIRE(y != nullptr || r_out != nullptr, "allreduce_add_layernorm: no output pointer");
+  DJV_REQUIRE(seq >= 0, "allreduce_add_layernorm: negative exchange number %d", seq);
+  DJV_REQUIRE(B >= 1 && B <= DJV_MAX_BATCH && d >= 8 && d % 8 == 0 && d / 8 <= EX_CLUSTER * EX_THREADS * 2,
               "allreduce_add_layernorm: bad B=%d d=%d", B, d);
   DJV_REQUIRE((size_t)B * d * 2 <= c->slot_bytes, "allreduce_add_layernorm: %zu bytes exceed the slot (%zu)",
               (size_t)B * d * 2, c->slot_bytes);
-  DJV_REQUIRE(aligned16(y) && (!partial || aligned16(partial)) && aligned16(gamma) && aligned16(beta) &&
-                  (!r_out || aligned16(r_out)) && (!residual || aligned16(residual)),
+  DJV_REQUIRE((!y || aligned16(y)) && (!partial || aligned16(partial)) && (!gamma || aligned16(gamma)) &&
+                  (!beta || aligned16(beta)) && (!r_out || aligned16(r_out)) && (!residual || aligned16(residual)),
               "allreduce_add_layernorm: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   c->last_stream = st;
-#define DJV_AR_CALL(NCH_)                                                                                       \
-  djv::launch_kernel(allreduce_add_layernorm_kernel<NCH_>, 1, LN_THREADS, 0, st, c->bufs_dev, c->epoch_dev,     \
-                     c->rank, c->world, c->slot_bytes, static_cast<__half *>(y), static_cast<__half *>(r_out), \
-                     static_cast<const __half *>(partial), static_cast<const __half *>(residual),              \
-                     static_cast<const __half *>(gamma), static_cast<const __half *>(beta), B, d, eps)
-  DJV_LN_DISPATCH(d / 8, DJV_AR_CALL);
-#undef DJV_AR_CALL
+  FoldArgs a = fold_args(c, seq);
+  a.partial = static_cast<const __half *>(partial);
+  a.residual = static_cast<const __half *>(residual);
+  a.r_out = static_cast<__half *>(r_out);
+  a.gamma = static_cast<const __half *>(gamma);
+  a.beta = static_cast<const __half *>(beta);
+  a.eps = eps;
+  a.y = static_cast<__half *>(y);
+  a.refill = (flags & DJV_EXCHANGE_REFILL) ? 1 : 0;
+  a.B = B;
+  a.d = d;
+  const dim3 grid(EX_CLUSTER, B);
+  if (d / 8 <= EX_CLUSTER * EX_THREADS)
+    djv::launch_kernel(exchange_layernorm_kernel<1>, grid, EX_THREADS, 0, st, a);
+  else
+    djv::launch_kernel(exchange_layernorm_kernel<2>, grid, EX_THREADS, 0, st, a);
   count_launch();
   return check_launch("allreduce_add_layernorm");
 }

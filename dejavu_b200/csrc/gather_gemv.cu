@@ -15,6 +15,15 @@
 
 namespace djv {
 
+// the same products on the bulk-copy ring pipeline (mlp_ring.cu)
+int ring_fc1(__half *y, const __half *w, const __half *x, const void *idx, const __half *bias, int B, int N, int M,
+             long long ldw, int idx64, int act, cudaStream_t st);
+int ring_fc2(__half *y, const __half *w, const __half *h, const void *idx, const __half *bias, int B, int N, int M,
+             long long ldw, int idx64, void *scratch, cudaStream_t st, const PushTarget &push);
+// Development knob DJV_RING_GEMV (read at every call): route djv_gather_gemv / djv_gather_transposed_gemv calls
+// of at most that many rows through the ring pipeline when the shape allows it. 0 = never.
+static int ring_gemv_rows() { return env_int("DJV_RING_GEMV", 0); }
+static bool ring_shape_ok(int B, int N, int M) { return djv_mlp_sparse_fused_supported(B, N, M) != 0; }
 
 // -------------------------------------------------------------------------------------------
 // rowdot. A block has 8 warps split into 8/WPR groups of WPR warps; a group owns ROWS rows at a
@@ -263,6 +272,12 @@ extern "C" int djv_gather_gemv(void *y, const void *w, const void *x, const void
   DJV_REQUIRE(act >= DJV_ACT_ID && act <= DJV_ACT_SQUARED_RELU, "gather_gemv: unknown activation %d", act);
   if (M == 0) return DJV_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M <= ring_gemv_rows() && ring_shape_ok(B, N, M)) {
+    rc = ring_fc1(static_cast<__half *>(y), static_cast<const __half *>(w), static_cast<const __half *>(x), idx,
+                  static_cast<const __half *>(bias), B, N, M, ldw, idx_is_64, act, st);
+    if (rc) return rc;
+    return check_launch("gather_gemv");
+  }
   // Enough activation rows make this a real small-N contraction: tensor cores. Measured cross-over on B200
   // (d = 12288): above 8 rows always; for 3..8 rows only when there are >= 256 tiles of 16 gathered rows
   // (the CUDA-core kernel, one slice of <= 8 rows at a time, wins on short index lists).
@@ -320,6 +335,12 @@ extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x,
               scratch_bytes);
     return DJV_ERR_SCRATCH;
   }
+  if (M <= ring_gemv_rows() && ring_shape_ok(B, N, M) && scratch_bytes >= djv_mlp_sparse_fused_scratch_bytes(B, N, M)) {
+    rc = ring_fc2(static_cast<__half *>(y), static_cast<const __half *>(w), static_cast<const __half *>(x), idx,
+                  static_cast<const __half *>(bias), B, N, M, ldw, idx_is_64, scratch, st, PushTarget{});
+    if (rc) return rc;
+    return check_launch("gather_transposed_gemv");
+  }
   for (int b0 = 0; b0 < B; b0 += 4) {
     const int bs = (B - b0 < 4) ? (B - b0) : 4;
     rc = rowaxpy_slice(bs, static_cast<__half *>(y) + (size_t)b0 * N, static_cast<const __half *>(w),
@@ -332,12 +353,13 @@ extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x,
 }
 
 // fc2 with the result sent into every rank's receive buffer of the tensor-parallel exchange instead of y
-// (see push.cuh); the all-reduce kernel that follows is called with partial == NULL.
-extern "C" int djv_gather_transposed_gemv_push(djv_comm *comm, const void *w, const void *x, const void *idx,
+// as exchange number `seq` of the step (see push.cuh); the consumer of that exchange is called with
+// partial == NULL.
+extern "C" int djv_gather_transposed_gemv_push(djv_comm *comm, int seq, const void *w, const void *x, const void *idx,
                                                const void *bias, int B, int N, int M, long long ldw,
                                                int idx_is_64, void *scratch, size_t scratch_bytes,
                                                void *stream) {
-  DJV_REQUIRE(comm != nullptr, "gather_transposed_gemv_push: null comm");
+  DJV_REQUIRE(comm != nullptr && seq >= 0, "gather_transposed_gemv_push: null comm or negative exchange number");
   DJV_REQUIRE(M >= 1, "gather_transposed_gemv_push: needs at least one row");
   int rc = check_common("gather_transposed_gemv_push", w /* y unused */, w, x, B, N, M, ldw);
   if (rc) return rc;
@@ -352,7 +374,7 @@ extern "C" int djv_gather_transposed_gemv_push(djv_comm *comm, const void *w, co
   }
   rc = rowaxpy_slice(B, nullptr, static_cast<const __half *>(w), static_cast<const __half *>(x), idx,
                      static_cast<const __half *>(bias), scratch, M, N, ldw, idx_is_64,
-                     static_cast<cudaStream_t>(stream), push_target(comm));
+                     static_cast<cudaStream_t>(stream), push_target(comm, seq));
   if (rc) return rc;
   count_launch();
   return check_launch("gather_transposed_gemv_push");

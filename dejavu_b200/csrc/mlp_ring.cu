@@ -1,0 +1,574 @@
+// Sparse MLP in ONE pass over the gathered rows, and the tensor-parallel exchange + LayerNorm in front of it:
+//
+//   x   = LayerNorm(sum over ranks of the attention partials + residual)      (optional prologue, exchange.cuh)
+//   h_m = relu(W1[idx[m], :] . x + b1[idx[m]])   rounded to fp16
+//   y   = sum_m h_m * W2t[idx[m], :] + b2         -> y, or straight into every rank's receive buffer
+//
+// Work split. A thread-block cluster of 8 blocks owns a contiguous range of the index list; block j of the
+// cluster owns columns [j*d/8, (j+1)*d/8) of BOTH matrices. Per gathered row a block therefore streams two
+// segments of d/8 halves (3 KB each at d = 12288): the dot product of row m is the sum of the 8 blocks' partial
+// dots (exchanged through distributed shared memory, once per batch of rows), and the block accumulates
+// h_m * W2t[idx[m], its columns] into d/8 fp32 sums held in registers (8 per thread and activation row).
+// The contribution of row m to y depends on h_m only, so no grid-wide step is needed between the two products.
+//
+// Memory pipeline. Segments are brought into a shared-memory ring by bulk asynchronous copies (ring.cuh): two
+// batches of up to 32 rows are in flight per block (up to ~190 KB per multiprocessor), issued by one warp,
+// each row's pair of segments completing on its own mbarrier. When the caller promises that the index list is
+// complete before the launch (djv_set_early_weight_prefetch), the first two batches are issued BEFORE the
+// kernel waits for its predecessor: the weight stream then overlaps the predecessor's tail, the NVLink trip of
+// the exchange and the LayerNorm. For a 512-row index list everything the kernel reads is in flight at once.
+//
+// Reduction over clusters: per-cluster partial sums go to scratch, the last block to arrive for a column
+// segment adds them in cluster order (deterministic) and finishes (bias, fp16, store or push).
+// The same kernel runs fc1 alone (MODE 1) and fc2 alone (MODE 2).
+//
+// Algorithmic bytes (fp16, int32 idx): fused 2*M*d*2 + M*(2 + 4) + d*2 + 2*B*d*2.
+#include <mutex>
+
+#include "exchange.cuh"
+#include "ring.cuh"
+
+namespace djv {
+
+constexpr int MR_THREADS = 384;
+constexpr int MR_WARPS = MR_THREADS / WARP;
+constexpr int MR_C = 8;          // blocks per cluster = column segments
+constexpr int MR_MAX_NSH = 32;   // rows per batch (half of the ring)
+constexpr int MR_MAX_RG = 8;     // row groups of the second product
+constexpr int MR_MAX_B = 4;
+constexpr int MR_MAX_CLUSTERS = 32;
+constexpr int MR_COUNTER_BYTES = 4096;
+// shared-memory layout (bytes from the start of dynamic shared memory)
+constexpr int MR_OFF_BARS = 0;      // 2 * nsh mbarriers
+constexpr int MR_OFF_PD = 512;      // [2][B][nsh] partial dots of this block
+constexpr int MR_OFF_HS = 1536;     // [B][nsh] activations of the batch
+constexpr int MR_OFF_MISC = 2048;   // statistics, flags
+constexpr int MR_OFF_X = 2304;      // [B][seg] halves, then the ring (128-byte aligned)
+constexpr int MR_SMEM_BUDGET = 200 * 1024;
+
+__device__ unsigned g_ring_timeouts;  // bounded waits on bulk copies that ran out (never, in a healthy run)
+
+struct RingArgs {
+  const __half *w1, *w2;  // (Z,N) rows of stride ldw1 / ldw2; w2 is W2 transposed
+  long long ldw1, ldw2;
+  const void *idx;
+  int idx64;
+  const __half *bias1, *bias2;
+  int M, N, act;
+  const __half *x;     // (B,N) input of the first product (MODE 0, 1) unless fold
+  const __half *h_in;  // (B,M) input of the second product (MODE 2)
+  int fold;            // x comes from the exchange
+  FoldArgs f;
+  __half *y;           // (B,N) (MODE 0, 2) or (B,M) (MODE 1); unused when pushing
+  PushTarget push;
+  float *partial;
+  unsigned *counters;
+  int rpc, nsh, early;
+};
+
+__device__ __forceinline__ float apply_act_rt(int act, float v) {
+  switch (act) {
+    case DJV_ACT_RELU: return apply_act<DJV_ACT_RELU>(v);
+    case DJV_ACT_GELU: return apply_act<DJV_ACT_GELU>(v);
+    case DJV_ACT_GELU_APPROX: return apply_act<DJV_ACT_GELU_APPROX>(v);
+    case DJV_ACT_SQUARED_RELU: return apply_act<DJV_ACT_SQUARED_RELU>(v);
+    default: return v;
+  }
+}
+
+template <int B, int MODE>
+__global__ void __cluster_dims__(MR_C, 1, 1) __launch_bounds__(MR_THREADS, 1) mlp_ring_kernel(RingArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
+  const int crank = (int)cluster.block_rank();
+  const int cl = blockIdx.x / MR_C, n_cl = gridDim.x / MR_C;
+  const int seg = a.N / MR_C, CH = seg / 8;
+  const unsigned seg_bytes = (unsigned)seg * 2u;
+  const unsigned stage_bytes = (MODE == 0 ? 2u : 1u) * seg_bytes;
+  const int nsh = a.nsh;
+
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + MR_OFF_BARS);
+  float *pd = reinterpret_cast<float *>(smem + MR_OFF_PD);
+  float *hs = reinterpret_cast<float *>(smem + MR_OFF_HS);
+  float *misc = reinterpret_cast<float *>(smem + MR_OFF_MISC);
+  float *st = misc, *stf = misc + 16, *red = misc + 24;  // [4][4], [4][2], [12]
+  int *flags_s = reinterpret_cast<int *>(misc + 40);     // [0] fold failed, [1] ring wait ran out, [2] last block
+  __half *x_s = reinterpret_cast<__half *>(smem + MR_OFF_X);
+  unsigned char *ring = smem + ((MR_OFF_X + (MODE == 2 ? 0 : B * seg * 2) + 127) & ~127);
+
+  const int m_begin = min(a.M, cl * a.rpc), m_end = min(a.M, m_begin + a.rpc);
+  const int nrows = m_end - m_begin;
+  const int nbatch = (nrows + nsh - 1) / nsh;
+
+  if (tid < 2 * nsh) mbar_init(&bars[tid], 1);
+  if (tid == 0) {
+    flags_s[1] = 0;
+    flags_s[2] = 0;
+  }
+  mbar_fence_init();
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // warp 0: start the copies of batch bi (lane l takes rows l, l + 32 of the batch)
+  auto issue = [&](int bi) {
+    const int r0 = bi * nsh, nr = min(nsh, nrows - r0), sbase = (bi & 1) * nsh;
+    for (int s = lane; s < nr; s += WARP) {
+      const long long r = load_index(a.idx, m_begin + r0 + s, a.idx64);
+      uint64_t *bar = &bars[sbase + s];
+      unsigned char *dst = ring + (size_t)(sbase + s) * stage_bytes;
+      mbar_arrive_expect_tx(bar, stage_bytes);
+      if (MODE != 2) {
+        bulk_load(dst, a.w1 + r * a.ldw1 + (size_t)crank * seg, seg_bytes, bar);
+        dst += seg_bytes;
+      }
+      if (MODE != 1) bulk_load(dst, a.w2 + r * a.ldw2 + (size_t)crank * seg, seg_bytes, bar);
+    }
+  };
+  if (a.early && warp == 0) {
+    if (nbatch > 0) issue(0);
+    if (nbatch > 1) issue(1);
+  }
+  FoldRegs<B> fr;
+  const int c_lo = crank * CH, c_hi = c_lo + CH;
+  if (MODE != 2 && a.fold) fold_fetch_affine<MR_THREADS, B>(fr, a.f, c_lo, c_hi, 0, B);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!a.early && warp == 0) {
+    if (nbatch > 0) issue(0);
+    if (nbatch > 1) issue(1);
+  }
+
+  // ---- this block's columns of the input rows ------------------------------------------------
+  bool input_ok = true;
+  if (MODE != 2) {
+    if (a.fold) {
+      input_ok = exchange_fold<MR_THREADS, B>(a.f, cluster, MR_C, c_lo, c_hi, 0, B, cl == 0, x_s, crank,
+                                              cl == 0 ? MR_C : 0, fr, red, st, stf, &flags_s[0]);
+    } else {
+      for (int item = tid; item < B * CH; item += MR_THREADS) {
+        const int b = item / CH, c = item % CH;
+        reinterpret_cast<uint4 *>(x_s)[item] = ld_cached16(a.x + (size_t)b * a.N + (size_t)(c_lo + c) * 8);
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- main loop over batches of rows ----------------------------------------------------------
+  const int RG = min(MR_THREADS / CH, MR_MAX_RG);
+  const int rg = tid / CH, cc = tid % CH;  // second product: this thread's row group and 16-byte column chunk
+  const bool colthread = rg < RG;
+  float acc[B][8];
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[b][e] = 0.f;
+  bool ring_ok = true;
+  const uint4 *xs4 = reinterpret_cast<const uint4 *>(x_s);
+
+  for (int bi = 0; bi < nbatch; ++bi) {
+    const int r0 = bi * nsh, nr = min(nsh, nrows - r0), sbase = (bi & 1) * nsh;
+    const unsigned par = (unsigned)(bi >> 1) & 1u;
+    float *pdb = pd + (size_t)(bi & 1) * B * nsh;
+    if (MODE != 2) {
+      // first product: a warp per row, partial dot over this block's columns
+      for (int s = warp; s < nr; s += MR_WARPS) {
+        ring_ok = mbar_wait(&bars[sbase + s], par) && ring_ok;
+        const uint4 *w = reinterpret_cast<const uint4 *>(ring + (size_t)(sbase + s) * stage_bytes);
+        float p[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) p[b] = 0.f;
+        for (int c = lane; c < CH; c += WARP) {
+          const uint4 wv = w[c];
+#pragma unroll
+          for (int b = 0; b < B; ++b) p[b] = dot8(wv, xs4[b * CH + c], p[b]);
+        }
+#pragma unroll
+        for (int b = 0; b < B; ++b) p[b] = warp_sum(p[b]);
+        if (lane == 0) {
+#pragma unroll
+          for (int b = 0; b < B; ++b) pdb[b * nsh + s] = p[b];
+        }
+      }
+      cluster.sync();  // every block's partial dots of this batch are in its shared memory
+      if (MODE == 1 && warp == 0 && bi + 2 < nbatch) {  // fc1 alone: the batch's stages are free already
+        fence_proxy_async_smem();
+        issue(bi + 2);
+      }
+    }
+    // activations of the batch (every block of the cluster computes the same values, in the same order)
+    for (int item = tid; item < nr * B; item += MR_THREADS) {
+      const int s = item / B, b = item % B;
+      const int m = m_begin + r0 + s;
+      float v;
+      if (MODE == 2) {
+        v = __half2float(a.h_in[(size_t)b * a.M + m]);
+      } else {
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < MR_C; ++j) sum += cluster.map_shared_rank(pdb, j)[b * nsh + s];
+        if (a.bias1 != nullptr) sum += __half2float(a.bias1[load_index(a.idx, m, a.idx64)]);
+        const __half hv = __float2half_rn(apply_act_rt(a.act, sum));  // h is an fp16 tensor between the products
+        if (MODE == 1 && crank == 0) a.y[(size_t)b * a.M + m] = hv;
+        v = __half2float(hv);
+      }
+      hs[b * nsh + s] = v;
+    }
+    if (MODE == 1) continue;  // (pd is double-buffered: the next cluster barrier orders its reuse)
+    __syncthreads();
+    // second product: thread (rg, cc) adds rows rg, rg + RG, ... of the batch into its 8 columns
+    if (colthread) {
+      for (int s = rg; s < nr; s += RG) {
+        // complete already (MODE 0); the wait makes the copied bytes visible to this thread
+        ring_ok = mbar_wait(&bars[sbase + s], par) && ring_ok;
+        const uint4 wv = *reinterpret_cast<const uint4 *>(ring + (size_t)(sbase + s) * stage_bytes +
+                                                          (MODE == 0 ? seg_bytes : 0u) + (size_t)cc * 16);
+        const float2 w0 = h2f(wv.x), w1 = h2f(wv.y), w2 = h2f(wv.z), w3 = h2f(wv.w);
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const float hb = hs[b * nsh + s];
+          acc[b][0] = fmaf(hb, w0.x, acc[b][0]);
+          acc[b][1] = fmaf(hb, w0.y, acc[b][1]);
+          acc[b][2] = fmaf(hb, w1.x, acc[b][2]);
+          acc[b][3] = fmaf(hb, w1.y, acc[b][3]);
+          acc[b][4] = fmaf(hb, w2.x, acc[b][4]);
+          acc[b][5] = fmaf(hb, w2.y, acc[b][5]);
+          acc[b][6] = fmaf(hb, w3.x, acc[b][6]);
+          acc[b][7] = fmaf(hb, w3.y, acc[b][7]);
+        }
+      }
+    }
+    __syncthreads();  // the batch's stages and hs are free
+    if (warp == 0 && bi + 2 < nbatch) {
+      fence_proxy_async_smem();
+      issue(bi + 2);
+    }
+  }
+  if (!ring_ok) flags_s[1] = 1;
+  cluster.sync();  // no block leaves (or reuses the ring) while a peer may still read its shared memory
+  if (flags_s[1] != 0 && tid == 0) atomicAdd(&g_ring_timeouts, 1u);
+  const bool ok = input_ok && flags_s[1] == 0;
+  if (MODE == 1) return;
+
+  // ---- row groups -> block -> clusters -> result ---------------------------------------------------
+  float *redv = reinterpret_cast<float *>(ring);  // [RG][B][seg]; every copy into the ring has completed
+  if (colthread) {
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      float4 *dst = reinterpret_cast<float4 *>(redv + ((size_t)rg * B + b) * seg + (size_t)cc * 8);
+      dst[0] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
+      dst[1] = make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]);
+    }
+  }
+  __syncthreads();
+  const int gcol0 = crank * seg;
+  size_t piece_off = 0;
+  if (a.push.bufs != nullptr) piece_off = push_piece_offset(a.push);
+  auto emit = [&](int b, int c, float (&v)[8]) {
+    const int gcol = gcol0 + c * 8;
+    if (a.bias2 != nullptr) {
+      float t8[8];
+      unpack8f(ld_cached16(a.bias2 + gcol), t8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += t8[e];
+    }
+    const uint4 packed = round8(v);
+    if (!ok) return;
+    if (a.push.bufs != nullptr)
+      push16(a.push, piece_off, (size_t)b * a.N + gcol, packed);
+    else
+      *reinterpret_cast<uint4 *>(a.y + (size_t)b * a.N + gcol) = packed;
+  };
+  for (int item = tid; item < B * CH; item += MR_THREADS) {
+    const int b = item / CH, c = item % CH;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    for (int g = 0; g < RG; ++g) {
+      const float4 *src = reinterpret_cast<const float4 *>(redv + ((size_t)g * B + b) * seg + (size_t)c * 8);
+      const float4 lo = src[0], hi = src[1];
+      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+    }
+    if (n_cl == 1) {
+      emit(b, c, v);
+    } else {
+      float4 *dst = reinterpret_cast<float4 *>(a.partial + ((size_t)cl * B + b) * a.N + gcol0 + c * 8);
+      __stcg(dst, make_float4(v[0], v[1], v[2], v[3]));
+      __stcg(dst + 1, make_float4(v[4], v[5], v[6], v[7]));
+    }
+  }
+  if (n_cl == 1) return;
+  // several clusters: the last block to arrive for this column segment adds their sums in cluster order
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned ticket = atomicAdd(&a.counters[crank], 1u);
+    flags_s[2] = (ticket == (unsigned)n_cl - 1u) ? 1 : 0;
+  }
+  __syncthreads();
+  if (flags_s[2] == 0) return;
+  __threadfence();
+  for (int item = tid; item < B * CH; item += MR_THREADS) {
+    const int b = item / CH, c = item % CH;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    for (int k = 0; k < n_cl; ++k) {
+      const float4 *src = reinterpret_cast<const float4 *>(a.partial + ((size_t)k * B + b) * a.N + gcol0 + c * 8);
+      const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+    }
+    emit(b, c, v);
+  }
+  if (tid == 0) a.counters[crank] = 0;  // ready for the next launch
+}
+
+}  // namespace djv
+
+using namespace djv;
+
+namespace {
+
+struct RingPlan {
+  int n_cl, rpc, nsh;
+  size_t smem;
+};
+
+inline size_t ring_fixed_bytes(int B, int N, int mode) {
+  const int seg = N / MR_C;
+  return (size_t)((MR_OFF_X + (mode == 2 ? 0 : B * seg * 2) + 127) & ~127);
+}
+
+inline size_t ring_smem_bytes(int B, int N, int mode, int nsh) {
+  const int seg = N / MR_C, CH = seg / 8;
+  const size_t stage = (size_t)(mode == 0 ? 2 : 1) * seg * 2;
+  int RG = MR_THREADS / CH;
+  if (RG > MR_MAX_RG) RG = MR_MAX_RG;
+  size_t ring = (size_t)2 * nsh * stage;
+  const size_t redv = mode == 1 ? 0 : (size_t)RG * B * seg * sizeof(float);
+  if (ring < redv) ring = redv;
+  return ring_fixed_bytes(B, N, mode) + ring;
+}
+
+template <int B, int MODE>
+int ring_max_clusters(size_t smem) {
+  // clusters of this kernel the device holds at once, per shared-memory size (a handful of distinct sizes)
+  static std::mutex mu;
+  static size_t keys[16];
+  static int vals[16];
+  static int n = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n; ++i)
+    if (keys[i] == smem) return vals[i];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(MR_C, 1, 1);
+  cfg.blockDim = dim3(MR_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  int got = 0;
+  if (cudaOccupancyMaxActiveClusters(&got, mlp_ring_kernel<B, MODE>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    got = 0;
+  }
+  if (got <= 0) got = sm_count() / MR_C * 7 / 8;  // fall-back: what the cluster granularity of a GPC loses
+  if (n < 16) {
+    keys[n] = smem;
+    vals[n] = got;
+    ++n;
+  }
+  return got;
+}
+
+template <int B, int MODE>
+int ring_prepare() {
+  static int rc = [] {
+    cudaError_t e = cudaFuncSetAttribute(mlp_ring_kernel<B, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         MR_SMEM_BUDGET + 8192);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return 1;
+    }
+    return 0;
+  }();
+  return rc;
+}
+
+template <int B, int MODE>
+int ring_launch(RingArgs a, cudaStream_t st) {
+  if (ring_prepare<B, MODE>() != 0) {
+    set_error("mlp_ring: cannot raise the kernel's shared-memory limit");
+    return DJV_ERR_CUDA;
+  }
+  const int seg = a.N / MR_C;
+  const size_t stage = (size_t)(MODE == 0 ? 2 : 1) * seg * 2;
+  const size_t fixed = ring_fixed_bytes(B, a.N, MODE);
+  int nsh_max = (int)((MR_SMEM_BUDGET - fixed) / (2 * stage));
+  if (nsh_max > MR_MAX_NSH) nsh_max = MR_MAX_NSH;
+  if (nsh_max < 1) {
+    set_error("mlp_ring: N=%d rows do not fit the shared-memory ring", a.N);
+    return DJV_ERR_UNSUPPORTED;
+  }
+  static const int k_cl = env_int("DJV_RING_CLUSTERS", 0);  // development knob
+  int maxcl = k_cl > 0 ? k_cl : ring_max_clusters<B, MODE>(ring_smem_bytes(B, a.N, MODE, nsh_max));
+  if (maxcl > MR_MAX_CLUSTERS) maxcl = MR_MAX_CLUSTERS;
+  if (maxcl < 1) maxcl = 1;
+  // at least 4 rows per cluster; then even shares
+  int n_cl = ceil_div(a.M, 4);
+  if (n_cl > maxcl) n_cl = maxcl;
+  const int rpc = ceil_div(a.M, n_cl);
+  n_cl = ceil_div(a.M, rpc);
+  int nsh = ceil_div(rpc, 2);
+  if (nsh > nsh_max) nsh = nsh_max;
+  a.rpc = rpc;
+  a.nsh = nsh;
+  const size_t smem = ring_smem_bytes(B, a.N, MODE, nsh);
+  djv::launch_kernel(mlp_ring_kernel<B, MODE>, dim3(n_cl * MR_C), dim3(MR_THREADS), smem, st, a);
+  count_launch();
+  return DJV_OK;
+}
+
+template <int MODE>
+int ring_dispatch(int B, const RingArgs &a, cudaStream_t st) {
+  switch (B) {
+    case 1: return ring_launch<1, MODE>(a, st);
+    case 2: return ring_launch<2, MODE>(a, st);
+    case 3: return ring_launch<3, MODE>(a, st);
+    case 4: return ring_launch<4, MODE>(a, st);
+  }
+  set_error("mlp_ring: batch %d outside [1,%d]", B, MR_MAX_B);
+  return DJV_ERR_INVALID;
+}
+
+int ring_check(const char *op, int B, int N, int M, long long ld1, long long ld2, const void *w1, const void *w2,
+               void *scratch, size_t scratch_bytes) {
+  DJV_REQUIRE(B >= 1 && B <= MR_MAX_B, "%s: batch %d outside [1,%d]", op, B, MR_MAX_B);
+  DJV_REQUIRE(N >= 64 && N % (8 * MR_C) == 0 && N / (8 * MR_C) <= MR_THREADS,
+              "%s: N=%d must be a multiple of %d and at most %d", op, N, 8 * MR_C, 8 * MR_C * MR_THREADS);
+  DJV_REQUIRE(M >= 1, "%s: needs at least one row", op);
+  DJV_REQUIRE((!w1 || (ld1 >= N && ld1 % 8 == 0 && aligned16(w1))) && (!w2 || (ld2 >= N && ld2 % 8 == 0 && aligned16(w2))),
+              "%s: weights must be 16-byte aligned with row strides >= N that are multiples of 8", op);
+  const size_t need = djv_mlp_sparse_fused_scratch_bytes(B, N, M);
+  if (scratch == nullptr || scratch_bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
+    set_error("%s: scratch needs %zu bytes, 256-byte aligned (got %zu)", op, need, scratch_bytes);
+    return DJV_ERR_SCRATCH;
+  }
+  return DJV_OK;
+}
+
+void ring_scratch(RingArgs &a, void *scratch) {
+  a.counters = reinterpret_cast<unsigned *>(scratch);
+  a.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + MR_COUNTER_BYTES);
+}
+
+}  // namespace
+
+extern "C" int djv_mlp_sparse_fused_supported(int B, int N, int M) {
+  return B >= 1 && B <= MR_MAX_B && N >= 64 && N % (8 * MR_C) == 0 && N / (8 * MR_C) <= MR_THREADS && M >= 1;
+}
+
+extern "C" size_t djv_mlp_sparse_fused_scratch_bytes(int B, int N, int M) {
+  if (B < 1 || N < 8 || M < 0) return 0;
+  return MR_COUNTER_BYTES + (size_t)MR_MAX_CLUSTERS * B * N * sizeof(float);
+}
+
+extern "C" unsigned djv_mlp_ring_timeouts(void) {
+  unsigned v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_ring_timeouts, sizeof(v)) != cudaSuccess) {
+    cudaGetLastError();
+    return ~0u;
+  }
+  return v;
+}
+
+extern "C" int djv_mlp_sparse_fused(void *y, const void *w1, const void *w2t, const void *x, const void *idx,
+                                    const void *bias1, const void *bias2, int B, int N, int M, long long ldw1,
+                                    long long ldw2t, int idx_is_64, void *scratch, size_t scratch_bytes,
+                                    void *stream) {
+  DJV_REQUIRE(y && w1 && w2t && x && idx, "mlp_sparse_fused: null pointer");
+  int rc = ring_check("mlp_sparse_fused", B, N, M, ldw1, ldw2t, w1, w2t, scratch, scratch_bytes);
+  if (rc) return rc;
+  DJV_REQUIRE(aligned16(x) && aligned16(y) && (!bias2 || aligned16(bias2)),
+              "mlp_sparse_fused: x, y and bias2 must be 16-byte aligned");
+  RingArgs a{};
+  a.w1 = static_cast<const __half *>(w1);
+  a.w2 = static_cast<const __half *>(w2t);
+  a.ldw1 = ldw1; a.ldw2 = ldw2t;
+  a.idx = idx; a.idx64 = idx_is_64;
+  a.bias1 = static_cast<const __half *>(bias1);
+  a.bias2 = static_cast<const __half *>(bias2);
+  a.M = M; a.N = N; a.act = DJV_ACT_RELU;
+  a.x = static_cast<const __half *>(x);
+  a.y = static_cast<__half *>(y);
+  a.early = early_prefetch() ? 1 : 0;
+  ring_scratch(a, scratch);
+  rc = ring_dispatch<0>(B, a, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return check_launch("mlp_sparse_fused");
+}
+
+extern "C" int djv_mlp_sparse_fused_exchange(djv_comm *comm, int seq_in, int flags, int seq_out, void *y,
+                                             void *r_out, const void *residual, const void *gamma,
+                                             const void *beta, float eps, const void *w1, const void *w2t,
+                                             const void *idx, const void *bias1, const void *bias2, int B, int N,
+                                             int M, long long ldw1, long long ldw2t, int idx_is_64, void *scratch,
+                                             size_t scratch_bytes, void *stream) {
+  DJV_REQUIRE(comm && w1 && w2t && idx && gamma && beta, "mlp_sparse_fused_exchange: null pointer");
+  DJV_REQUIRE(seq_in >= 0 && (seq_out >= 0 || y != nullptr),
+              "mlp_sparse_fused_exchange: needs an input exchange and an output (exchange number or y)");
+  int rc = ring_check("mlp_sparse_fused_exchange", B, N, M, ldw1, ldw2t, w1, w2t, scratch, scratch_bytes);
+  if (rc) return rc;
+  DJV_REQUIRE((size_t)B * N * 2 <= comm->slot_bytes, "mlp_sparse_fused_exchange: %zu bytes exceed the slot (%zu)",
+              (size_t)B * N * 2, comm->slot_bytes);
+  DJV_REQUIRE((!y || aligned16(y)) && (!r_out || aligned16(r_out)) && (!residual || aligned16(residual)) &&
+                  aligned16(gamma) && aligned16(beta) && (!bias2 || aligned16(bias2)),
+              "mlp_sparse_fused_exchange: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  comm->last_stream = st;
+  RingArgs a{};
+  a.w1 = static_cast<const __half *>(w1);
+  a.w2 = static_cast<const __half *>(w2t);
+  a.ldw1 = ldw1; a.ldw2 = ldw2t;
+  a.idx = idx; a.idx64 = idx_is_64;
+  a.bias1 = static_cast<const __half *>(bias1);
+  a.bias2 = static_cast<const __half *>(bias2);
+  a.M = M; a.N = N; a.act = DJV_ACT_RELU;
+  a.fold = 1;
+  a.f = fold_args(comm, seq_in);
+  a.f.residual = static_cast<const __half *>(residual);
+  a.f.r_out = static_cast<__half *>(r_out);
+  a.f.gamma = static_cast<const __half *>(gamma);
+  a.f.beta = static_cast<const __half *>(beta);
+  a.f.eps = eps;
+  a.f.refill = (flags & DJV_EXCHANGE_REFILL) ? 1 : 0;
+  a.f.B = B;
+  a.f.d = N;
+  a.y = static_cast<__half *>(y);
+  if (seq_out >= 0) a.push = push_target(comm, seq_out);
+  a.early = early_prefetch() ? 1 : 0;
+  ring_scratch(a, scratch);
+  rc = ring_dispatch<0>(B, a, st);
+  if (rc) return rc;
+  return check_launch("mlp_sparse_fused_exchange");
+}
+
+// fc1 / fc2 alone on the same pipeline (used by djv_gather_gemv / djv_gather_transposed_gemv for short index
+// lists, where bytes in flight matter most)
+namespace djv {
+int ring_fc1(__half *y, const __half *w, const __half *x, const void *idx, const __half *bias, int B, int N, int M,
+             long long ldw, int idx64, int act, cudaStream_t st) {
+  RingArgs a{};
+  a.w1 = w; a.ldw1 = ldw; a.idx = idx; a.idx64 = idx64; a.bias1 = bias;
+  a.M = M; a.N = N; a.act = act; a.x = x; a.y = y;
+  a.early = (idx == nullptr || early_prefetch()) ? 1 : 0;
+  return ring_dispatch<1>(B, a, st);
+}
+int ring_fc2(__half *y, const __half *w, const __half *h, const void *idx, const __half *bias, int B, int N, int M,
+             long long ldw, int idx64, void *scratch, cudaStream_t st, const PushTarget &push) {
+  RingArgs a{};
+  a.w2 = w; a.ldw2 = ldw; a.idx = idx; a.idx64 = idx64; a.bias2 = bias;
+  a.M = M; a.N = N; a.h_in = h; a.y = y; a.push = push;
+  a.early = (idx == nullptr || early_prefetch()) ? 1 : 0;
+  ring_scratch(a, scratch);
+  return ring_dispatch<2>(B, a, st);
+}
+}  // namespace djv

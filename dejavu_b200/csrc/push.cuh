@@ -1,8 +1,8 @@
-// Pieces of the tensor-parallel exchange that kernels other than the all-reduce itself use: the comm object,
-// and the stores with which a kernel that has just finished part of this rank's partial sum sends it
-// straight into every rank's receive buffer (see comm.cu for the protocol). A GEMV kernel that pushes its
-// result this way overlaps the NVLink trip with its own tail and with the launch of the all-reduce kernel,
-// which then only waits for the pieces, adds them and normalises.
+// Pieces of the tensor-parallel exchange that kernels other than the exchange kernel itself use: the comm
+// object, the slot arithmetic, and the stores with which a kernel that has just finished part of this rank's
+// partial sum sends it straight into every rank's receive buffer (see exchange.cuh for the protocol). A GEMV
+// kernel that pushes its result this way overlaps the NVLink trip with its own tail and with the launch of
+// the kernel that consumes the exchange, which then only waits for the pieces, adds them and normalises.
 #pragma once
 #include "common.cuh"
 
@@ -11,32 +11,41 @@ struct djv_comm {
   size_t slot_bytes;
   // device-side tables (cudaMalloc'ed by djv_comm_create)
   void **bufs_dev;
-  unsigned *epoch_dev;  // [0] epoch, [1] status
+  unsigned *ctl_dev;  // [0] exchanges completed in earlier steps (advanced by djv_comm_end_step), [1] status
   cudaStream_t last_stream;
 };
 
 namespace djv {
 
 constexpr int AR_MAX_WORLD = 8;
-constexpr int AR_SLOTS = 3;
+// Receive slots per rank. Exchange number e (counted since the comm was created) uses slot e % 4. The kernel on
+// the main stream that consumes exchange e refills slot (e + 2) % 4 with the sentinel: that slot held exchange
+// e - 2, whose readers on this rank are finished (its main consumer precedes this kernel on the stream; a side
+// consumer of e - 2 produces something the consumer of e waited for), and no peer writes it again before
+// exchange e + 2, which a peer can only start after it has received this rank's piece of e + 1, sent after this
+// kernel ended. Slots (e + 1) % 4 and (e + 3) % 4 are left alone: peers may already be filling the first and a
+// side stream may still be reading the second.
+constexpr int AR_SLOTS = 4;
 constexpr unsigned AR_SENTINEL2 = 0x80008000u;  // two fp16 -0.0
 
 // where a kernel sends its part of the partial sum; bufs == nullptr: nowhere (plain output)
 struct PushTarget {
-  void *const *bufs;             // device table of every rank's receive buffer
-  const unsigned *epoch_status;  // [0] epoch: read-only here, advanced by the all-reduce kernel
+  void *const *bufs;    // device table of every rank's receive buffer
+  const unsigned *ctl;  // [0] exchanges completed in earlier steps: read-only here
   int rank, world;
   size_t slot_bytes;
+  int seq;              // number of this exchange inside the current step
 };
 
-inline PushTarget push_target(const djv_comm *c) {
+inline PushTarget push_target(const djv_comm *c, int seq) {
   PushTarget t{};
   if (c) {
     t.bufs = c->bufs_dev;
-    t.epoch_status = c->epoch_dev;
+    t.ctl = c->ctl_dev;
     t.rank = c->rank;
     t.world = c->world;
     t.slot_bytes = c->slot_bytes;
+    t.seq = seq;
   }
   return t;
 }
@@ -69,10 +78,13 @@ __device__ __forceinline__ bool arrived16(const uint4 &v) {
   return !(has_sentinel2(v.x) || has_sentinel2(v.y) || has_sentinel2(v.z) || has_sentinel2(v.w));
 }
 
-// byte offset of piece [rank] of the current slot inside every receive buffer
+// slot of exchange `seq` of the current step (ctl[0] is stable for the whole step)
+__device__ __forceinline__ int exchange_slot(const unsigned *ctl, int seq) {
+  return (int)((ctl[0] + (unsigned)seq) % (unsigned)AR_SLOTS);
+}
+// byte offset of piece [rank] of this exchange's slot inside every receive buffer
 __device__ __forceinline__ size_t push_piece_offset(const PushTarget &t) {
-  const unsigned epoch = t.epoch_status[0];
-  return ((size_t)(epoch % AR_SLOTS) * t.world + t.rank) * t.slot_bytes;
+  return ((size_t)exchange_slot(t.ctl, t.seq) * t.world + t.rank) * t.slot_bytes;
 }
 
 // 8 (or 4) consecutive fp16 of this rank's partial, element offset `elem` (a multiple of 8 / 4), to every rank

@@ -205,6 +205,8 @@ class GPTModel(nn.Module):
         hidden_states, _ = last._add_norm(hidden_states, residual, self.ln_f, partial_in)
         if hidden_states.is_cuda:
             join_side_streams(hidden_states.device)  # the last layer's look-ahead results have no consumer
+            if self.comm is not None:
+                self.comm.end_step()  # every kernel of the step that reads the exchange is queued before this
         return hidden_states
 
 

@@ -44,6 +44,12 @@ FUSE_STEP_OPEN = os.environ.get("DJV_FUSE_STEP_OPEN", "1") != "0"
 PUSH_PARTIALS = os.environ.get("DJV_PUSH_PARTIALS", "1") != "0"
 # kernels whose index list is known to be complete prefetch weights before their PDL wait (development knob)
 EARLY_PREFETCH = os.environ.get("DJV_EARLY_PREFETCH", "1") != "0"
+# with a comm: exchange + residual + LayerNorm + fc1 + ReLU + fc2 (+ send) of a block in one kernel (development knob)
+FUSED_MLP = os.environ.get("DJV_FUSED_MLP", "1") != "0"
+# where the main stream joins the side stream that selects this layer's MLP rows: "attend" = before the attention
+# kernel (the fused MLP kernel then follows out_proj with a single programmatic edge and streams its weights while
+# out_proj runs), "mlp" = right before the MLP (development knob)
+MLP_IDX_JOIN = os.environ.get("DJV_MLP_IDX_JOIN", "attend")
 _SIDE_STREAMS: dict = {}
 _SIDE_DIRTY: dict = {}  # device index -> names of side streams forked since the last join
 
@@ -291,6 +297,37 @@ class ParallelFusedMLPDejavu(nn.Module):
         return out, mlp_logit
 
 
+    def can_fuse_after_exchange(self, partial, idx) -> bool:
+        """Whether decode_after_exchange applies: a comm that producers push into, a sparse step, and a shape
+        the one-pass kernel takes."""
+        if not (FUSED_MLP and self.push_comm is not None and idx is not None and self.activation == "relu"):
+            return False
+        if partial.dim() != 3 or partial.size(1) != 1 or self.push_comm.pushed_seq(partial) is None:
+            return False
+        return bool(_lib.load().djv_mlp_sparse_fused_supported(partial.size(0), partial.size(2), idx.numel()))
+
+    def decode_after_exchange(self, partial, residual, norm, idx):
+        """The block's second half in one kernel: residual = sum over ranks(partial) + residual;
+        x = norm(residual); out = fc2(relu(fc1(x)[idx])) sent as the next exchange. The look-ahead predictor
+        (fused_dense_sparse_dejavu.py:942-949) takes its own copy of the new residual from the same exchange on
+        the side stream, so that it does not wait for this kernel. Returns (out, residual, mlp_logit)."""
+        comm = self.push_comm
+        B, _, d = partial.shape
+        p2 = partial.view(B, d)
+        r2 = None if residual is None else residual.reshape(B, d)
+        mlp_logit = None
+        if self.has_predictor and self.run_predictor:
+            seq_in = comm.pushed_seq(p2)
+            with _side(partial, "mlp", after=residual) as done:
+                _, r_side = comm.allreduce_add_layernorm(p2, r2, None, None, norm.eps, refill=False, seq=seq_in)
+                mlp_logit = self.sp(r_side)
+                done(mlp_logit)
+        with ops.indices_ready(EARLY_PREFETCH and getattr(idx, "_ready_event", None) is not None):
+            out, r = ops.mlp_sparse_after_exchange(comm, p2, r2, norm.weight, norm.bias, norm.eps, self.fc1.weight,
+                                                   self.fc2.weight_t, idx, self.fc1.bias, self.fc2.bias, push=True)
+        return out.view(B, 1, d), r.view(B, 1, d), mlp_logit
+
+
 class ParallelFusedMLP(ParallelFusedMLPDejavu):
     """The dense MLP of the comparator model (fused_dense_sparse_dejavu.py:696-780): no predictor; decode
     GEMVs go through cuBLAS (torch), which is the dense fp16 decode the sparse path is measured against."""
@@ -438,10 +475,11 @@ class ParallelMHASparseAttMlp(nn.Module):
         n_eff_ptr = state.data_ptr() + 4 * 2
         with ops.indices_ready(early):
             if self.push_comm is not None:
-                call("djv_out_proj_sparse_push", self.push_comm.handle, self.out_proj.weight.data_ptr(),
+                seq = self.push_comm.next_seq()
+                call("djv_out_proj_sparse_push", self.push_comm.handle, seq, self.out_proj.weight.data_ptr(),
                      b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n,
                      hd, n, st)
-                self.push_comm.note_pushed(out)
+                self.push_comm.note_pushed(out, seq)
             else:
                 call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
                      eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
@@ -481,10 +519,16 @@ class ParallelMHASparseAttMlp(nn.Module):
         if decoding:
             assert do_token_generation
             _wait_ready(head_idx)
-            # the head predictor forks after the QKV projection: its GEMVs then overlap the attention kernel,
-            # which leaves HBM mostly idle, instead of taking the multiprocessors just before the projection
+
+            def between():
+                # the head predictor forks after the QKV projection: its GEMVs then overlap the attention kernel,
+                # which leaves HBM mostly idle, instead of taking the multiprocessors just before the projection
+                predict_heads()
+                if MLP_IDX_JOIN == "attend" and self.push_comm is not None:
+                    _wait_ready(mlp_idx)
+
             out = self._decode_attention(x, head_idx if self.sparse_attention else None, inference_params,
-                                         between=predict_heads)
+                                         between=between)
         else:
             predict_heads()
             out = self.out_proj(self._prompt_attention(x, inference_params))
@@ -578,8 +622,13 @@ class BlockMlpAttSparse(nn.Module):
             hidden_states, mlp_idx = self.mixer(hidden_states, residual=residual, mlp_sp_logit=mlp_sp_logit,
                                                 **mixer_kwargs)
             next_att_idx = None
-        hidden_states, residual = self._add_norm(hidden_states, residual, self.norm2, self.comm is not None)
-        hidden_states, next_mlp_sp_logit = self.mlp(hidden_states, residual, mlp_idx)
+        if self.comm is not None and self.mlp.can_fuse_after_exchange(hidden_states, mlp_idx):
+            _wait_ready(mlp_idx)
+            hidden_states, residual, next_mlp_sp_logit = self.mlp.decode_after_exchange(hidden_states, residual,
+                                                                                          self.norm2, mlp_idx)
+        else:
+            hidden_states, residual = self._add_norm(hidden_states, residual, self.norm2, self.comm is not None)
+            hidden_states, next_mlp_sp_logit = self.mlp(hidden_states, residual, mlp_idx)
         if self.returns_att_idx:
             return hidden_states, residual, next_mlp_sp_logit, next_att_idx
         return hidden_states, residual, next_mlp_sp_logit

@@ -130,12 +130,16 @@ def gather_transposed_gemv(
         assert x.dtype == bias.dtype, f"Input and bias must have the same dtype, got {x.dtype} and {bias.dtype}"
     idx, idx64 = _idx_args(idx)
     output = torch.empty(batch, N, device=x.device, dtype=x.dtype)
-    need = _lib.load().djv_gather_transposed_gemv_scratch_bytes(batch, N, M)
+    lib = _lib.load()
+    need = max(lib.djv_gather_transposed_gemv_scratch_bytes(batch, N, M),
+               lib.djv_mlp_sparse_fused_scratch_bytes(batch, N, M) if batch <= 4 else 0)
     scratch = _scratch(need, x.device)
     if push_comm is not None and M >= 1 and batch <= 4:
-        call("djv_gather_transposed_gemv_push", push_comm.handle, weight.data_ptr(), x.data_ptr(), idx.data_ptr(),
-             _ptr(bias), batch, N, M, weight.stride(0), idx64, scratch.data_ptr(), scratch.numel(), _stream())
-        push_comm.note_pushed(output)
+        seq = push_comm.next_seq()
+        call("djv_gather_transposed_gemv_push", push_comm.handle, seq, weight.data_ptr(), x.data_ptr(),
+             idx.data_ptr(), _ptr(bias), batch, N, M, weight.stride(0), idx64, scratch.data_ptr(), scratch.numel(),
+             _stream())
+        push_comm.note_pushed(output, seq)
         return output
     call("djv_gather_transposed_gemv", output.data_ptr(), weight.data_ptr(), x.data_ptr(), idx.data_ptr(),
          _ptr(bias), batch, N, M, weight.stride(0), idx64, scratch.data_ptr(), scratch.numel(), _stream())
@@ -156,9 +160,10 @@ def dense_transposed_gemv(x: torch.Tensor, weight_t: torch.Tensor, bias: Optiona
     need = _lib.load().djv_gather_transposed_gemv_scratch_bytes(batch, N, M)
     scratch = _scratch(need, x.device)
     if push_comm is not None and batch <= 4:
-        call("djv_gather_transposed_gemv_push", push_comm.handle, weight_t.data_ptr(), x.data_ptr(), None,
+        seq = push_comm.next_seq()
+        call("djv_gather_transposed_gemv_push", push_comm.handle, seq, weight_t.data_ptr(), x.data_ptr(), None,
              _ptr(bias), batch, N, M, weight_t.stride(0), 0, scratch.data_ptr(), scratch.numel(), _stream())
-        push_comm.note_pushed(output)
+        push_comm.note_pushed(output, seq)
         return output
     call("djv_gather_transposed_gemv", output.data_ptr(), weight_t.data_ptr(), x.data_ptr(), None, _ptr(bias),
          batch, N, M, weight_t.stride(0), 0, scratch.data_ptr(), scratch.numel(), _stream())
@@ -166,10 +171,62 @@ def dense_transposed_gemv(x: torch.Tensor, weight_t: torch.Tensor, bias: Optiona
 
 
 def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None, push_comm=None):
-    """x (batch, d); W1 (4d, d); W2t (4d, d) = W2 transposed, contiguous; bias1 (4d); bias2 (d)."""
-    x = gather_gemv(x, W1, idx, bias1, activation="relu")
-    x = gather_transposed_gemv(x, W2t, idx, bias2, push_comm=push_comm)
-    return x
+    """x (batch, d); W1 (4d, d); W2t (4d, d) = W2 transposed, contiguous; bias1 (4d); bias2 (d).
+    One kernel and one pass over the gathered rows when the shape allows it (batch <= 4, d % 64 == 0),
+    otherwise gather_gemv followed by gather_transposed_gemv."""
+    batch, N = x.shape
+    (M,) = idx.shape
+    fused = (push_comm is None and x.is_cuda and x.dtype == torch.float16 and W1.dtype == torch.float16
+             and W2t.dtype == torch.float16 and W1.stride(1) == 1 and W2t.stride(1) == 1
+             and W1.shape[1] == N and W2t.shape[1] == N
+             and _lib.load().djv_mlp_sparse_fused_supported(batch, N, M))
+    if not fused:
+        x = gather_gemv(x, W1, idx, bias1, activation="relu")
+        return gather_transposed_gemv(x, W2t, idx, bias2, push_comm=push_comm)
+    _require_cuda(x, W1, W2t, idx, bias1, bias2)
+    x = x.contiguous()
+    idx, idx64 = _idx_args(idx)
+    if bias1 is not None:
+        bias1 = bias1.contiguous()
+        assert bias1.shape == (W1.shape[0],) and bias1.dtype == x.dtype
+    if bias2 is not None:
+        bias2 = bias2.contiguous()
+        assert bias2.shape == (N,) and bias2.dtype == x.dtype
+    output = torch.empty(batch, N, device=x.device, dtype=x.dtype)
+    need = _lib.load().djv_mlp_sparse_fused_scratch_bytes(batch, N, M)
+    scratch = _scratch(need, x.device)
+    call("djv_mlp_sparse_fused", output.data_ptr(), W1.data_ptr(), W2t.data_ptr(), x.data_ptr(), idx.data_ptr(),
+         _ptr(bias1), _ptr(bias2), batch, N, M, W1.stride(0), W2t.stride(0), idx64, scratch.data_ptr(),
+         scratch.numel(), _stream())
+    return output
+
+
+def mlp_sparse_after_exchange(comm, partial, residual, norm_weight, norm_bias, eps, W1, W2t, idx, bias1=None,
+                              bias2=None, push=True):
+    """The second half of a decoder block in one launch:
+        r = sum over ranks(partial) + residual;  x = LayerNorm(r);  out = mlp_sparse(x, W1, W2t, idx, bias1, bias2)
+    `partial` (batch, d) is a placeholder whose content its producer sent as an exchange of `comm`. With
+    `push` the result is sent as the next exchange (the returned `out` is then a placeholder for it), otherwise
+    it is stored. Returns (out, r)."""
+    batch, N = partial.shape
+    (M,) = idx.shape
+    seq_in = comm.take_pushed(partial)
+    assert seq_in is not None, "partial must have been sent by its producer"
+    _require_cuda(partial, residual, W1, W2t, idx, bias1, bias2)
+    idx, idx64 = _idx_args(idx)
+    out = torch.empty(batch, N, device=partial.device, dtype=partial.dtype)
+    r = torch.empty(batch, N, device=partial.device, dtype=partial.dtype)
+    need = _lib.load().djv_mlp_sparse_fused_scratch_bytes(batch, N, M)
+    scratch = _scratch(need, partial.device)
+    seq_out = comm.next_seq() if push else -1
+    call("djv_mlp_sparse_fused_exchange", comm.handle, seq_in, _lib.EXCHANGE_REFILL, seq_out,
+         None if push else out.data_ptr(), r.data_ptr(), _ptr(None if residual is None else residual.contiguous()),
+         norm_weight.data_ptr(), norm_bias.data_ptr(), float(eps), W1.data_ptr(), W2t.data_ptr(), idx.data_ptr(),
+         _ptr(bias1), _ptr(bias2), batch, N, M, W1.stride(0), W2t.stride(0), idx64, scratch.data_ptr(),
+         scratch.numel(), _stream())
+    if push:
+        comm.note_pushed(out, seq_out)
+    return out, r
 
 
 def qkv_proj_sparse(

@@ -110,6 +110,25 @@ int djv_mlp_sparse(void *y, void *h, const void *w1, const void *w2t, const void
                    long long ldw2t, int idx_is_64, void *scratch, size_t scratch_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The same sparse MLP in ONE kernel and one pass over the gathered rows: the block that streams row idx[m] of
+ * W1 and of W2t computes h_m = relu(w1[idx[m],:] . x + bias1[idx[m]]), rounds it to fp16 as the reference
+ * does between its two kernels (Dejavu/src/ops/triton/gather_gemv.py:233), and at once adds
+ * h_m * w2t[idx[m],:] to the output sums. Replaces mlp_sparse, gather_gemv.py:647-657 (two launches, a
+ * zero-fill and a cast there). Deterministic. 1 <= B <= 4, N % 64 == 0, N <= 24576, M >= 1
+ * (djv_mlp_sparse_fused_supported says whether a shape qualifies; use djv_mlp_sparse otherwise).
+ *   scratch: djv_mlp_sparse_fused_scratch_bytes(B,N,M) bytes, 256-byte aligned, first 4096 bytes ZERO before
+ *   the first call (left zero again); calls that share scratch must not overlap on the GPU.
+ * djv_mlp_ring_timeouts(): how many bounded waits on the kernel's own asynchronous copies ever ran out in
+ * this process (0 in a healthy run; synchronises).
+ * ------------------------------------------------------------------------------------------- */
+int djv_mlp_sparse_fused_supported(int B, int N, int M);
+size_t djv_mlp_sparse_fused_scratch_bytes(int B, int N, int M);
+unsigned djv_mlp_ring_timeouts(void);
+int djv_mlp_sparse_fused(void *y, const void *w1, const void *w2t, const void *x, const void *idx,
+                         const void *bias1, const void *bias2, int B, int N, int M, long long ldw1,
+                         long long ldw2t, int idx_is_64, void *scratch, size_t scratch_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Top-K index selection over one score vector.
  * Replaces mlp_sp_logit.topk(K, sorted=False) / att_sp_logit.topk(K) + .to(int32),
  * Dejavu/src/models/modules/mha_dejavu.py:1069, 1369, 1506-1507.
@@ -254,9 +273,22 @@ int djv_add_layernorm(void *y, void *r_out, const void *x, const void *residual,
  * djv_comm is created per process from peer-mapped buffers the host exchanged (CUDA IPC):
  *   bufs[r] : rank r's receive buffer of djv_comm_buffer_bytes(world, slot_bytes) bytes, mapped into this
  *             process; bufs[rank] is this rank's own and is initialised by djv_comm_create.
- * Every rank must have returned from djv_comm_create before any rank runs djv_allreduce_add_layernorm.
+ * world = 1 is allowed (one buffer, this process's own): the same kernels then run on a single GPU.
+ * Every rank must have returned from djv_comm_create before any rank runs an exchange.
+ *
+ * Numbering. The exchanges of one decode step are numbered seq = 0, 1, 2, ... by the caller, identically on
+ * every rank; a producer (*_push) and every consumer of the same exchange pass the same seq. After the last
+ * kernel of the step that touches the exchange (all streams joined) the caller runs
+ * djv_comm_end_step(comm, number of exchanges of the step), and numbering restarts at 0. seq is a launch
+ * argument, so a captured CUDA graph of one step replays correctly. Consecutive exchanges use consecutive
+ * receive slots (4 per rank).
+ * Exactly ONE consumer of each exchange, on the stream that also runs the producers, passes
+ * DJV_EXCHANGE_REFILL: it recycles the slot used two exchanges earlier. Further consumers of the same exchange
+ * (on other streams) must not pass it, and whatever they produce must be waited for by the refilling consumer
+ * of exchange seq + 2 (in the decode step: the look-ahead predictor's result is needed two exchanges later).
  * ------------------------------------------------------------------------------------------- */
 typedef struct djv_comm djv_comm;
+#define DJV_EXCHANGE_REFILL 1
 /* Set-up helpers (these DO allocate / free with cudaMalloc / cudaFree and zero the memory): a buffer
  * that is the base of its own allocation, as CUDA IPC handles require. */
 int djv_ipc_alloc(size_t bytes, void **dev_ptr_out);
@@ -269,21 +301,38 @@ int djv_comm_create(djv_comm **out, int rank, int world, void *const *bufs, size
 int djv_comm_destroy(djv_comm *comm);
 /* Reads the device status word (synchronises the stream the comm last ran on). */
 int djv_comm_status(djv_comm *comm);
+/* Closes a step: the next step's exchange 0 follows this step's exchange n_exchanges - 1 (one tiny kernel). */
+int djv_comm_end_step(djv_comm *comm, int n_exchanges, void *stream);
 /* The two producers of a rank's partial sums can send them into every rank's receive buffer themselves, as
- * they finish each piece, so that the NVLink trip overlaps their tail and the launch of the all-reduce:
- * same arguments as djv_gather_transposed_gemv / djv_out_proj_sparse with `comm` in place of y (B <= 4,
- * B*N*2 <= slot_bytes). The djv_allreduce_add_layernorm call that follows passes partial = NULL.
- * Exactly one producer call per all-reduce call, on the same stream, before it. */
-int djv_gather_transposed_gemv_push(djv_comm *comm, const void *w, const void *x, const void *idx,
+ * they finish each piece, so that the NVLink trip overlaps their tail and the launch of the consumer:
+ * same arguments as djv_gather_transposed_gemv / djv_out_proj_sparse with `comm, seq` in place of y (B <= 4,
+ * B*N*2 <= slot_bytes). The consumers of that exchange pass partial = NULL.
+ * Exactly one producer call per exchange, on the same stream as its refilling consumer, before it. */
+int djv_gather_transposed_gemv_push(djv_comm *comm, int seq, const void *w, const void *x, const void *idx,
                                     const void *bias, int B, int N, int M, long long ldw, int idx_is_64,
                                     void *scratch, size_t scratch_bytes, void *stream);
-int djv_out_proj_sparse_push(djv_comm *comm, const void *w, const void *x, const int32_t *head_idx,
+int djv_out_proj_sparse_push(djv_comm *comm, int seq, const void *w, const void *x, const int32_t *head_idx,
                              const int32_t *n_active_dev, const void *bias, int B, int d, int nheads, int hd,
                              int nnz, void *stream);
-/* partial: this rank's (B,d) fp16 partial sums, or NULL when a *_push call has sent them. B*d*2 <= slot_bytes. */
-int djv_allreduce_add_layernorm(djv_comm *comm, void *y, void *r_out, const void *partial,
-                                const void *residual, const void *gamma, const void *beta, int B,
-                                int d, float eps, void *stream);
+/* Consumer as a kernel of its own (one cluster of 8 blocks per row).
+ * partial: this rank's (B,d) fp16 partial sums, or NULL when a *_push call has sent them. B*d*2 <= slot_bytes.
+ * gamma = beta = NULL: no LayerNorm, y = r (either of y, r_out may be NULL). flags: DJV_EXCHANGE_REFILL. */
+int djv_allreduce_add_layernorm(djv_comm *comm, int seq, int flags, void *y, void *r_out, const void *partial,
+                                const void *residual, const void *gamma, const void *beta, int B, int d,
+                                float eps, void *stream);
+/* The second half of a decoder block in one launch (typedef above):
+ *   r = sum_ranks(pieces of exchange seq_in) + residual;  x = LN(r) * gamma + beta;
+ *   out = djv_mlp_sparse_fused(x, ...)  ->  sent as exchange seq_out (seq_out >= 0), or stored to y.
+ * Replaces the chain all_reduce -> residual add -> norm2 -> mlp_sparse -> (all_reduce), i.e.
+ * Dejavu/src/models/modules/mha_dejavu.py:1498, block_dejavu.py:625-636,
+ * Dejavu/src/ops/fused_dense_sparse_dejavu.py:914-940. The weight stream of the MLP starts before the wait on
+ * the peers (see djv_set_early_weight_prefetch). r_out (B,N) or NULL receives r. flags: DJV_EXCHANGE_REFILL.
+ * Shapes and scratch as djv_mlp_sparse_fused; B*N*2 <= slot_bytes. */
+int djv_mlp_sparse_fused_exchange(djv_comm *comm, int seq_in, int flags, int seq_out, void *y, void *r_out,
+                                  const void *residual, const void *gamma, const void *beta, float eps,
+                                  const void *w1, const void *w2t, const void *idx, const void *bias1,
+                                  const void *bias2, int B, int N, int M, long long ldw1, long long ldw2t,
+                                  int idx_is_64, void *scratch, size_t scratch_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -15,11 +15,19 @@ def tiny_config(mlp_K, att_K, n_layer=4):
     return apply_sparsity_knobs(cfg, mlp_K, att_K, att_K)
 
 
-def build(cfg, cuda, seed=0):
+def build(cfg, cuda, seed=0, local_exchange=False):
+    """local_exchange: route the block's hand-overs through a one-rank exchange object, which turns on the
+    kernels a tensor-parallel run uses (producers that send, the exchange + LayerNorm consumer, the one-launch
+    second half of a block) on a single GPU."""
     from dejavu_b200.gpt import GPTLMHeadModel
 
     model = GPTLMHeadModel(cfg, device=cuda, dtype=torch.float16).eval()
-    return model.init_random(seed, std=0.05)
+    model.init_random(seed, std=0.05)
+    if local_exchange:
+        from dejavu_b200.comm import TensorParallelComm
+
+        model.transformer.enable_fused_allreduce(TensorParallelComm(None, cuda, max_bytes=cfg.hidden_size * 2))
+    return model
 
 
 def record_selections(model):
@@ -37,11 +45,14 @@ def record_selections(model):
     return rec, handles
 
 
-@pytest.mark.parametrize("mlp_K,att_K", [(256, 2), (256, 4), (1024, 2), (1024, 4)])
-def test_decode_matches_oracle(cuda, mlp_K, att_K):
-    """Sparse MLP + sparse attention, sparse MLP only, sparse attention only, dense."""
+@pytest.mark.parametrize("mlp_K,att_K,local_exchange", [(256, 2, False), (256, 4, False), (1024, 2, False),
+                                                       (1024, 4, False), (256, 2, True), (256, 4, True),
+                                                       (1024, 2, True)])
+def test_decode_matches_oracle(cuda, mlp_K, att_K, local_exchange):
+    """Sparse MLP + sparse attention, sparse MLP only, sparse attention only, dense; and the same through the
+    exchange kernels (one rank)."""
     cfg = tiny_config(mlp_K, att_K)
-    model = build(cfg, cuda)
+    model = build(cfg, cuda, local_exchange=local_exchange)
     oracle = OracleDecoder(model.state_dict(), cfg)
     gen = torch.Generator().manual_seed(0)
     P, steps = 9, 36  # crosses two 16-step lazy-K/V windows
@@ -57,7 +68,7 @@ def test_decode_matches_oracle(cuda, mlp_K, att_K):
     for h in handles:
         h.remove()
     # the hooks fired once for the prompt pass (no selections) and once per decode step
-    model2 = build(cfg, cuda)
+    model2 = build(cfg, cuda, local_exchange=local_exchange)
     rec2, handles2 = record_selections(model2)
     from dejavu_b200.generation import InferenceParams, allocate_kv_cache
 
@@ -81,11 +92,16 @@ def test_decode_matches_oracle(cuda, mlp_K, att_K):
         assert m.mixer.decode_status() == 0
     for h in handles2:
         h.remove()
+    for m in (model, model2):
+        if m.transformer.comm is not None:
+            assert m.transformer.comm.status() == 0
+            m.transformer.comm.close()
 
 
-def test_cuda_graph_decode_equals_eager(cuda):
+@pytest.mark.parametrize("local_exchange", [False, True])
+def test_cuda_graph_decode_equals_eager(cuda, local_exchange):
     cfg = tiny_config(256, 2)
-    model = build(cfg, cuda)
+    model = build(cfg, cuda, local_exchange=local_exchange)
     gen = torch.Generator().manual_seed(1)
     ids = torch.randint(0, cfg.vocab_size, (1, 7), generator=gen).to(cuda)
     eager = model.generate(ids, max_length=7 + 40, cg=False, return_dict_in_generate=True, output_scores=True)
@@ -95,6 +111,21 @@ def test_cuda_graph_decode_equals_eager(cuda):
     assert torch.equal(graph.sequences, again.sequences)
     for a, b in zip(eager.scores, graph.scores):
         assert torch.equal(a, b), "graph replay must reproduce the eager step bit for bit"
+    if local_exchange:
+        # the exchange path computes the same function as the plain path: same logits within fp16 rounding for
+        # as long as both have decoded the same tokens (a near-tie may then send them different ways)
+        plain = build(cfg, cuda).generate(ids, max_length=7 + 40, cg=False, return_dict_in_generate=True,
+                                          output_scores=True)
+        same = 0
+        for t, (a, b) in enumerate(zip(plain.scores, eager.scores)):
+            if not torch.equal(plain.sequences[0, :7 + t], eager.sequences[0, :7 + t]):
+                break
+            assert torch.allclose(a.float(), b.float(), atol=3e-2, rtol=3e-2), f"step {t}"
+            same += 1
+        assert same >= 3
+        assert model.transformer.comm.status() == 0
+        del model._decoding_cache
+        model.transformer.comm.close()
 
 
 def test_state_dict_keys_follow_the_reference(cuda):

@@ -419,11 +419,15 @@ def test_attn_step_state_machine_vs_oracle(cuda, monkeypatch, nheads, hd, d, P, 
 # tensor-parallel exchange on one GPU: the peers' pieces are written by the test before the launch
 # (no kernel ever waits for another kernel), then a wait that nothing satisfies runs out
 # ---------------------------------------------------------------------------------------------
+SLOTS = 4
+SENT = -32768  # 0x8000 as int16: fp16 -0.0
+
+
 def _make_comm(lib, cuda, world, slot_bytes):
     import ctypes as C
 
     nbytes = lib.djv_comm_buffer_bytes(world, slot_bytes)
-    assert nbytes == 3 * world * slot_bytes
+    assert nbytes == SLOTS * world * slot_bytes
     bufs_t = [torch.zeros(nbytes // 2, dtype=torch.int16, device=cuda) for _ in range(world)]
     bufs = (C.c_void_p * world)(*[t.data_ptr() for t in bufs_t])
     comm = C.c_void_p()
@@ -433,49 +437,61 @@ def _make_comm(lib, cuda, world, slot_bytes):
     return comm, bufs_t
 
 
-@pytest.mark.parametrize("world,B,d", [(2, 1, 9216), (4, 2, 1024), (8, 1, 12288)])
+def _no_neg_zero(t):
+    t = t.clone()
+    t[t == 0] = 0.0
+    return t
+
+
+@pytest.mark.parametrize("world,B,d", [(2, 1, 9216), (4, 2, 1024), (8, 1, 12288), (1, 3, 256), (2, 1, 20480)])
 def test_allreduce_push_protocol_single_gpu(cuda, world, B, d):
     from dejavu_b200 import _lib
 
     lib = _lib.load()
     slot_bytes = (B * d * 2 + 255) // 256 * 256
     comm, bufs_t = _make_comm(lib, cuda, world, slot_bytes)
-    SENT = -32768  # 0x8000 as int16: fp16 -0.0
-    own = bufs_t[0].view(3, world, slot_bytes // 2)
+    own = bufs_t[0].view(SLOTS, world, slot_bytes // 2)
     assert bool((own == SENT).all()), "comm_create fills the rank's own buffer with the sentinel"
     gen = torch.Generator().manual_seed(world * d)
     gamma, beta = (1 + rand(gen, (d,), 0.1)).to(cuda), rand(gen, (d,), 0.1).to(cuda)
     st = torch.cuda.current_stream().cuda_stream
-    for step in range(5):
-        parts = rand(gen, (world, B, d))
-        parts[:, :, :3] = -0.0  # the sentinel value inside real data
-        res = rand(gen, (B, d))
-        slot = step % 3
-        for p in range(1, world):  # what rank p's kernel would have stored here (it sends -0.0 as +0.0)
-            piece = parts[p].clone()
-            piece[piece == 0] = 0.0
-            own[slot, p, :B * d] = piece.reshape(-1).view(torch.int16).to(cuda)
-        y = torch.empty(B, d, dtype=torch.float16, device=cuda)
-        r = torch.empty(B, d, dtype=torch.float16, device=cuda)
-        part0, resd = parts[0].to(cuda), res.to(cuda)
-        _lib.call("djv_allreduce_add_layernorm", comm, y.data_ptr(), r.data_ptr(), part0.data_ptr(), resd.data_ptr(),
-                  gamma.data_ptr(), beta.data_ptr(), B, d, 1e-5, st)
-        assert lib.djv_comm_status(comm) == 0
-        acc = torch.zeros(B, d)
-        for p in range(world):  # rank order, fp32, rounded once
-            acc += parts[p].float()
-        total = acc.half()
-        y_ref, r_ref = O.add_layernorm(total, res, gamma.cpu(), beta.cpu(), 1e-5)
-        assert torch.equal(r.cpu(), r_ref), "residual stream must be bit-exact"
-        close(y, y_ref, atol=2e-3)
-        # this rank's partial went to piece 0 of the same slot of every rank, with -0.0 sent as +0.0
-        sent = parts[0].clone()
-        sent[sent == 0] = 0.0
-        for p in range(world):
-            got = bufs_t[p].view(3, world, slot_bytes // 2)[slot, 0, :B * d].cpu()
-            assert torch.equal(got, sent.reshape(-1).view(torch.int16))
-        # the slot of the step before is free again
-        assert bool((own[(step + 2) % 3, :, :B * d] == SENT).all())
+    e = 0  # exchanges so far; steps of 3 exchanges each, so that the slot sequence wraps inside a step
+    for step in range(4):
+        for seq in range(3):
+            parts = rand(gen, (world, B, d))
+            parts[:, :, :3] = -0.0  # the sentinel value inside real data
+            res = rand(gen, (B, d))
+            slot = e % SLOTS
+            for p in range(1, world):  # what rank p's kernel would have stored here (it sends -0.0 as +0.0)
+                own[slot, p, :B * d] = _no_neg_zero(parts[p]).reshape(-1).view(torch.int16).to(cuda)
+            y = torch.empty(B, d, dtype=torch.float16, device=cuda)
+            r = torch.empty(B, d, dtype=torch.float16, device=cuda)
+            part0, resd = parts[0].to(cuda), res.to(cuda)
+            _lib.call("djv_allreduce_add_layernorm", comm, seq, _lib.EXCHANGE_REFILL, y.data_ptr(), r.data_ptr(),
+                      part0.data_ptr(), resd.data_ptr(), gamma.data_ptr(), beta.data_ptr(), B, d, 1e-5, st)
+            assert lib.djv_comm_status(comm) == 0
+            acc = torch.zeros(B, d)
+            for p in range(world):  # rank order, fp32, rounded once
+                acc += parts[p].float()
+            total = acc.half()
+            y_ref, r_ref = O.add_layernorm(total, res, gamma.cpu(), beta.cpu(), 1e-5)
+            assert torch.equal(r.cpu(), r_ref), "residual stream must be bit-exact"
+            close(y, y_ref, atol=2e-3)
+            # this rank's partial went to piece 0 of the same slot of every rank, with -0.0 sent as +0.0
+            for p in range(world):
+                got = bufs_t[p].view(SLOTS, world, slot_bytes // 2)[slot, 0, :B * d].cpu()
+                assert torch.equal(got, _no_neg_zero(parts[0]).reshape(-1).view(torch.int16))
+            # the slot used two exchanges ago is free again, whole extent; the one of the exchange before is not
+            assert bool((own[(slot + 2) % SLOTS] == SENT).all())
+            if e >= 1 and world > 1:
+                assert not bool((own[(slot + 3) % SLOTS, :, :B * d] == SENT).all())
+            # a second consumer of the same exchange (no refill, no LayerNorm) sees the same sum
+            r2 = torch.empty(B, d, dtype=torch.float16, device=cuda)
+            _lib.call("djv_allreduce_add_layernorm", comm, seq, 0, None, r2.data_ptr(), None, resd.data_ptr(), None,
+                      None, B, d, 0.0, st)
+            assert torch.equal(r2.cpu(), r_ref)
+            e += 1
+        _lib.call("djv_comm_end_step", comm, 3, st)
     lib.djv_comm_destroy(comm)
 
 
@@ -493,7 +509,8 @@ def test_allreduce_wait_runs_out_and_reports(cuda):
         d, dtype=torch.float16, device=cuda)
     y, r = torch.empty_like(x), torch.empty_like(x)
     st = torch.cuda.current_stream().cuda_stream
-    args = (comm, y.data_ptr(), r.data_ptr(), x.data_ptr(), None, g.data_ptr(), b.data_ptr(), 1, d, 1e-5, st)
+    args = (comm, 0, _lib.EXCHANGE_REFILL, y.data_ptr(), r.data_ptr(), x.data_ptr(), None, g.data_ptr(), b.data_ptr(),
+            1, d, 1e-5, st)
     t0 = time.time()
     _lib.call("djv_allreduce_add_layernorm", *args)
     assert lib.djv_comm_status(comm) == _lib.ERR_TIMEOUT
@@ -509,7 +526,7 @@ def test_allreduce_wait_runs_out_and_reports(cuda):
 
 @pytest.mark.parametrize("world", [2, 8])
 def test_push_producers_feed_the_allreduce(cuda, world):
-    """fc2 and out_proj store their result straight into every rank's receive buffer; the all-reduce that
+    """fc2 and out_proj store their result straight into every rank's receive buffer; the consumer that
     follows (partial = NULL) finds this rank's piece there. Peers' pieces are written by the test."""
     from dejavu_b200 import _lib, ops
 
@@ -517,25 +534,24 @@ def test_push_producers_feed_the_allreduce(cuda, world):
     d, M, Z, nheads, hd = 1024, 96, 512, 4, 128
     slot_bytes = d * 2
     comm, bufs_t = _make_comm(lib, cuda, world, slot_bytes)
-    own = bufs_t[0].view(3, world, d)
+    own = bufs_t[0].view(SLOTS, world, d)
     gen = torch.Generator().manual_seed(world)
     gamma, beta = (1 + rand(gen, (d,), 0.1)).to(cuda), rand(gen, (d,), 0.1).to(cuda)
     st = torch.cuda.current_stream().cuda_stream
 
-    def finish(step, mine, res):
-        """pre-fill the peers' pieces, run the all-reduce with partial = NULL, compare with the oracle"""
-        slot = step % 3
+    def finish(seq, mine, res):
+        """pre-fill the peers' pieces, run the consumer with partial = NULL, compare with the oracle"""
+        slot = seq % SLOTS
         for p in range(world):
-            got = bufs_t[p].view(3, world, d)[slot, 0].cpu().view(torch.float16)
+            got = bufs_t[p].view(SLOTS, world, d)[slot, 0].cpu().view(torch.float16)
             assert torch.equal(got, mine.reshape(-1)), f"piece of rank 0 in rank {p}'s buffer"
-        others = rand(gen, (world - 1, 1, d))
-        others[others == 0] = 0.0
+        others = _no_neg_zero(rand(gen, (world - 1, 1, d)))
         for p in range(1, world):
             own[slot, p] = others[p - 1].reshape(-1).view(torch.int16).to(cuda)
         y = torch.empty(1, d, dtype=torch.float16, device=cuda)
         r = torch.empty(1, d, dtype=torch.float16, device=cuda)
-        _lib.call("djv_allreduce_add_layernorm", comm, y.data_ptr(), r.data_ptr(), None, res.to(cuda).data_ptr(),
-                  gamma.data_ptr(), beta.data_ptr(), 1, d, 1e-5, st)
+        _lib.call("djv_allreduce_add_layernorm", comm, seq, _lib.EXCHANGE_REFILL, y.data_ptr(), r.data_ptr(), None,
+                  res.to(cuda).data_ptr(), gamma.data_ptr(), beta.data_ptr(), 1, d, 1e-5, st)
         assert lib.djv_comm_status(comm) == 0
         acc = mine.float().reshape(1, d).clone()
         for p in range(world - 1):
@@ -544,27 +560,25 @@ def test_push_producers_feed_the_allreduce(cuda, world):
         assert torch.equal(r.cpu(), r_ref)
         close(y, y_ref, atol=2e-3)
 
-    # step 0: fc2 (gather transposed GEMV)
+    # exchange 0: fc2 (gather transposed GEMV)
     W2t, b2 = rand(gen, (Z, d), 0.05), rand(gen, (d,), 0.1)
     h = rand(gen, (1, M))
     idx = torch.randperm(Z, generator=gen)[:M].sort().values.int()
-    want = ops.gather_transposed_gemv(h.to(cuda), W2t.to(cuda), idx.to(cuda), b2.to(cuda)).cpu()
-    want[want == 0] = 0.0
+    want = _no_neg_zero(ops.gather_transposed_gemv(h.to(cuda), W2t.to(cuda), idx.to(cuda), b2.to(cuda)).cpu())
     need = lib.djv_gather_transposed_gemv_scratch_bytes(1, d, M)
     scratch = torch.zeros(need, dtype=torch.uint8, device=cuda)
     Wd, hd_, idxd, bd = W2t.to(cuda), h.to(cuda), idx.to(cuda), b2.to(cuda)
-    _lib.call("djv_gather_transposed_gemv_push", comm, Wd.data_ptr(), hd_.data_ptr(), idxd.data_ptr(), bd.data_ptr(),
-              1, d, M, d, 0, scratch.data_ptr(), need, st)
+    _lib.call("djv_gather_transposed_gemv_push", comm, 0, Wd.data_ptr(), hd_.data_ptr(), idxd.data_ptr(),
+              bd.data_ptr(), 1, d, M, d, 0, scratch.data_ptr(), need, st)
     finish(0, want, rand(gen, (1, d)))
 
-    # step 1: out_proj over selected heads
+    # exchange 1: out_proj over selected heads
     Wo, bo = rand(gen, (d, nheads, hd), 0.05), rand(gen, (d,), 0.1)
     ctx = rand(gen, (1, nheads, hd))
     heads = torch.tensor([1, 3], dtype=torch.int32)
-    want = ops.out_proj_sparse(ctx.to(cuda), Wo.to(cuda), heads.to(cuda), bo.to(cuda)).cpu()
-    want[want == 0] = 0.0
+    want = _no_neg_zero(ops.out_proj_sparse(ctx.to(cuda), Wo.to(cuda), heads.to(cuda), bo.to(cuda)).cpu())
     Wod, ctxd, headsd, bod = Wo.to(cuda), ctx.to(cuda), heads.to(cuda), bo.to(cuda)
-    _lib.call("djv_out_proj_sparse_push", comm, Wod.data_ptr(), ctxd.data_ptr(), headsd.data_ptr(), None,
+    _lib.call("djv_out_proj_sparse_push", comm, 1, Wod.data_ptr(), ctxd.data_ptr(), headsd.data_ptr(), None,
               bod.data_ptr(), 1, d, nheads, hd, 2, st)
     finish(1, want, rand(gen, (1, d)))
     lib.djv_comm_destroy(comm)
