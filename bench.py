@@ -132,11 +132,11 @@ def kernel_timing(fns, iters=5):
     return e0.elapsed_time(e1) * 1e3 / (iters * len(fns))
 
 
-def kernel_rooflines(model, cfg, world, peak):
+def kernel_rooflines(model, cfg, world, peak, comm=None):
     """Times each hot kernel alone on every layer's own weights (64+ distinct matrices: far beyond L2)."""
     import torch
 
-    from dejavu_b200 import ops
+    from dejavu_b200 import _lib, ops
 
     layers = list(model.transformer.layers)
     dev = model.lm_head.weight.device
@@ -160,6 +160,22 @@ def kernel_rooflines(model, cfg, world, peak):
     us = kernel_timing([lambda l=l, i=i: ops.gather_transposed_gemv(h, l.mlp.fc2.weight_t, i, l.mlp.fc2.bias)
                         for l, i in zip(layers, idxs)])
     rec("gather_gemv_fc2", us, K * d * 2 + K * 2 + d * 2 + d * 2)
+    if _lib.load().djv_mlp_sparse_fused_supported(1, d, K):
+        us = kernel_timing([lambda l=l, i=i: ops.mlp_sparse(x, l.mlp.fc1.weight, l.mlp.fc2.weight_t, i, l.mlp.fc1.bias,
+                                                            l.mlp.fc2.bias) for l, i in zip(layers, idxs)])
+        rec("mlp_sparse_fused", us, 2 * K * d * 2 + K * 2 + K * 4 + d * 2 + 2 * d * 2)
+    norm = layers[0].norm1
+    us = kernel_timing([lambda: ops.add_layernorm(x, x, norm.weight, norm.bias, norm.eps) for _ in layers])
+    out["add_layernorm"] = {"us": round(us, 2)}
+    if comm is not None:
+        # the exchange + residual + LayerNorm kernel alone: every rank sends its piece, waits for the others'
+        def exchange_calls():
+            for _ in layers:
+                comm.allreduce_add_layernorm(x, x, norm.weight, norm.bias, norm.eps)
+            comm.end_step()
+
+        us = kernel_timing([exchange_calls]) / len(layers)
+        out["exchange_add_layernorm"] = {"us": round(us, 2), "note": "send + wait for all ranks + residual + LayerNorm"}
     if getattr(layers[0].mlp, "sp", None) is not None:
         R = layers[0].mlp.sp.fc0.weight.shape[0]
         t = torch.randn(1, R, device=dev, generator=gen).half()
@@ -180,7 +196,74 @@ def kernel_rooflines(model, cfg, world, peak):
     us = kernel_timing([lambda l=l, hh=hh: ops.out_proj_sparse(ctx, l.mixer.out_proj.weight.view(d, n, hd), hh,
                                                                l.mixer.out_proj.bias) for l, hh in zip(layers, heads)])
     rec("out_proj_head_sparse", us, d * a * hd * 2 + d * 2 + a * hd * 2 + d * 2)
+    S_att = 1024
+    kc = torch.randn(1, n, hd // 8, S_att, 8, device=dev, generator=gen).half()
+    vc = torch.randn(1, n, S_att, hd, device=dev, generator=gen).half()
+    q = torch.randn(1, n, hd, device=dev, generator=gen).half()
+    caches = [(kc.clone(), vc.clone()) for _ in range(8)]  # rotated: 8 x 2 x a x 1024 x 128 x 2 B
+    us = kernel_timing([lambda c=caches[i % 8], hh=hh: ops.decode_attention(q, c[0], c[1], hh, S_att, hd ** -0.5)
+                        for i, hh in enumerate(heads)])
+    rec("decode_attn_1024_tokens", us, 2 * a * S_att * hd * 2)
     return out
+
+
+def exchange_check(model, cfg, comm, dev, world, pg, steps=16, prompt_len=24):
+    """Correctness signal for the fused exchange path, before anything is timed: `steps` greedy tokens through
+    the plain path (NCCL all-reduce at world > 1, stand-alone residual + LayerNorm and two-kernel MLP at world 1),
+    then the same tokens teacher-forced through the exchange path (producers that send, exchange + LayerNorm
+    kernel, one-launch second half of a block). Logits must agree within fp16 rounding of the different
+    summation orders, and the arg-max must agree wherever the plain path's top-2 margin is decisive.
+    Raises (the run then exits non-zero) when they do not."""
+    import torch
+
+    from dejavu_b200.generation import InferenceParams, allocate_kv_cache
+
+    gen = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab_size, (1, prompt_len), generator=gen).to(dev)
+
+    def run(forced):
+        ip = InferenceParams(max_sequence_len=prompt_len + steps, max_batch_size=1,
+                             key_value_memory_dict=allocate_kv_cache(model, 1, prompt_len + steps, dev))
+        logits = [model(prompt, inference_params=ip).logits[0, -1, :cfg.vocab_size].float()]
+        ip.sequence_len_offset = prompt_len
+        toks = []
+        for t in range(steps):
+            tok = int(logits[-1].argmax()) if forced is None else forced[t]
+            toks.append(tok)
+            out = model(torch.tensor([[tok]], device=dev), position_ids=torch.tensor([[prompt_len + t]], device=dev),
+                        inference_params=ip).logits[0, -1, :cfg.vocab_size].float()
+            ip.sequence_len_offset += 1
+            logits.append(out)
+        return toks, logits
+
+    with torch.inference_mode():
+        model.transformer.enable_fused_allreduce(None)
+        toks, ref = run(None)
+        model.transformer.enable_fused_allreduce(comm)
+        _, got = run(toks)
+        model.transformer.enable_fused_allreduce(None)
+        torch.cuda.synchronize()
+    max_diff, decisive, agree = 0.0, 0, 0
+    for a, b in zip(ref[1:], got[1:]):
+        diff = float((a - b).abs().max())
+        max_diff = max(max_diff, diff)
+        top2 = a.topk(2).values
+        if float(top2[0] - top2[1]) > 4 * max(diff, 1e-3):
+            decisive += 1
+            agree += int(int(a.argmax()) == int(b.argmax()))
+    status = comm.status()
+    decode_status = max(abs(l.mixer.decode_status()) for l in model.transformer.layers)
+    result = {"steps": steps, "plain_path": "nccl all_reduce" if world > 1 else "stand-alone kernels",
+              "tokens_equal": agree == decisive, "decisive_steps": decisive,
+              "max_abs_logit_diff": round(max_diff, 5), "comm_status": status, "decode_status": decode_status}
+    flags = torch.tensor([int(result["tokens_equal"]), int(max_diff < 5e-2), int(status == 0)], device=dev)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=pg)
+    if int(flags.min()) != 1:
+        raise SystemExit(f"exchange path disagrees with the plain path: {result}")
+    return result
 
 
 def run_reference(args, cfg, mlp_K, att_K, world, rank):
@@ -309,10 +392,14 @@ def main():
     model = GPTLMHeadModel(cfg, process_group=pg, device=dev, dtype=torch.float16).eval()
     model.init_random(seed=0)
     comm = None
-    if world > 1 and args.fused_allreduce:
+    check = None
+    if args.fused_allreduce:
         from dejavu_b200.comm import TensorParallelComm
 
+        # world 1: a one-rank exchange object, so that the same kernels run (producers that send, exchange +
+        # LayerNorm, the one-launch second half of a block)
         comm = TensorParallelComm(pg, dev, max_bytes=cfg.hidden_size * 2)
+        check = exchange_check(model, cfg, comm, dev, world, pg)
         model.transformer.enable_fused_allreduce(comm)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
@@ -384,6 +471,8 @@ def main():
     })
     if args.n_layer:
         line["config"]["debug_n_layer"] = args.n_layer
+    if check is not None:
+        line["check"] = check
 
     if not args.no_dense:
         model.transformer.set_dense(True)
@@ -393,7 +482,7 @@ def main():
                          "launches_per_step": int(dper), "speedup_sparse_vs_dense": round(dms / ms, 3)}
 
     with torch.inference_mode():
-        kern = kernel_rooflines(model, cfg, world, peak)
+        kern = kernel_rooflines(model, cfg, world, peak, comm)
     top = kern["gather_gemv_fc1"]
     line["roofline"] = {"kernel": "rowdot_kernel (gather GEMV fc1)", "bound": "hbm", "achieved": top["achieved"],
                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": top["frac"],
@@ -413,9 +502,9 @@ def main():
                                 "kind": "port", "sample": r["sample"]}
     if rank == 0:
         emit(line)
+    if comm is not None:
+        comm.close()
     if world > 1:
-        if comm is not None:
-            comm.close()
         dist.barrier()
         dist.destroy_process_group()
 

@@ -65,12 +65,15 @@ SIGNATURES = {
     "djv_gather_transposed_gemv_push": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _sz, _vp]),
     "djv_out_proj_sparse_push": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "djv_comm_end_step": (_i, [_vp, _i, _vp]),
+    "djv_prefetch_rows_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp]),
+    "djv_prefetch_segments_l2": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _vp]),
     "djv_mlp_sparse_fused_supported": (_i, [_i, _i, _i]),
     "djv_mlp_sparse_fused_scratch_bytes": (_sz, [_i, _i, _i]),
     "djv_mlp_ring_timeouts": (C.c_uint, []),
-    "djv_mlp_sparse_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
+    "djv_mlp_ring_bad_indices": (C.c_uint, []),
+    "djv_mlp_sparse_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
     "djv_mlp_sparse_fused_exchange": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp,
-                                           _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
+                                           _i, _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
     "djv_set_early_weight_prefetch": (None, [_i]),
     "djv_comm_destroy": (_i, [_vp]),
     "djv_comm_status": (_i, [_vp]),

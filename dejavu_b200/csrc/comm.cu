@@ -28,7 +28,7 @@ __global__ void comm_end_step_kernel(unsigned *ctl, unsigned n) {
 template <int ITEMS>
 __global__ void __cluster_dims__(EX_CLUSTER, 1, 1) __launch_bounds__(EX_THREADS)
 exchange_layernorm_kernel(FoldArgs a) {
-  __shared__ float red[EX_THREADS / WARP];
+  __shared__ float red[EX_THREADS / WARP * 3];
   __shared__ float st[4], stf[2];
   __shared__ int failed_s;
   cg::cluster_group cluster = cg::this_cluster();
@@ -41,8 +41,9 @@ exchange_layernorm_kernel(FoldArgs a) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   FoldRegs<ITEMS> fr;
   fold_fetch_affine<EX_THREADS, ITEMS>(fr, a, c_lo, c_hi, row, 1);
+  const FoldCtx ctx = fold_begin(a);
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  exchange_fold<EX_THREADS, ITEMS>(a, cluster, EX_CLUSTER, c_lo, c_hi, row, 1, true, nullptr,
+  exchange_fold<EX_THREADS, ITEMS>(a, ctx, cluster, EX_CLUSTER, c_lo, c_hi, row, 1, true, nullptr,
                                    row * EX_CLUSTER + crank, (int)gridDim.y * EX_CLUSTER, fr, red, st, stf,
                                    &failed_s);
   cluster.sync();  // no block leaves while a peer may still read its statistics

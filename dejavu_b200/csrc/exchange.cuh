@@ -92,6 +92,23 @@ __device__ __forceinline__ uint4 round8(float (&f)[8]) {
   return *reinterpret_cast<uint4 *>(o);
 }
 
+// What a fold needs from device memory before it can address its slot. ctl[0] only changes between steps (one
+// tiny kernel after every stream of the step has been joined, many kernels before the first exchange of the next
+// step), and the table of buffers never changes: both may be read BEFORE the wait on the predecessor kernel,
+// which takes two dependent round trips to memory off the critical path. The status word is advisory.
+struct FoldCtx {
+  int slot;
+  bool dead;
+  char *local;
+};
+__device__ __forceinline__ FoldCtx fold_begin(const FoldArgs &a) {
+  FoldCtx c;
+  c.slot = exchange_slot(a.ctl, a.seq);
+  c.dead = a.ctl[1] != 0u;  // once a wait has run out the exchange is dead: later calls do not wait again
+  c.local = static_cast<char *>(a.bufs[a.rank]);
+  return c;
+}
+
 // Per-thread state of a fold: the values of the thread's chunks and their LayerNorm weights.
 template <int ITEMS>
 struct FoldRegs {
@@ -131,23 +148,24 @@ __device__ __forceinline__ void fold_fetch_affine(FoldRegs<ITEMS> &fr, const Fol
 //   writer   this cluster stores r_out / y to global memory (exactly one cluster per row should)
 //   x_s      shared memory, [nb][nseg * 8] halves: the block's part of the normalised rows (or null)
 //   refill_w / refill_n   this block is worker refill_w of refill_n of the slot refill (used when a.refill)
-//   red: THREADS / 32 floats, st: nb * 4 floats, stf: nb * 2 floats, failed_s: one int, all in shared memory
+//   red: THREADS / 32 * nb * 3 floats, st: nb * 4 floats, stf: nb * 2 floats, failed_s: one int, all in shared
+//   memory; ctx from fold_begin
+// CLUSTERED = false: the block covers the whole rows by itself (csize 1, no cluster-wide barrier is executed).
 // Contains cluster-wide barriers: every block of the cluster must call it, with the same nb.
 // The caller must keep the block alive (a cluster barrier) until its peers have read st.
 // Returns false when a wait ran out (the status word is set; outputs are then not written).
-template <int THREADS, int ITEMS>
-__device__ __forceinline__ bool exchange_fold(const FoldArgs &a, cg::cluster_group &cluster, int csize, int c_lo,
-                                              int c_hi, int b_lo, int nb, bool writer, __half *x_s,
-                                              int refill_w, int refill_n, FoldRegs<ITEMS> &fr, float *red,
-                                              float *st, float *stf, int *failed_s) {
+template <int THREADS, int ITEMS, bool CLUSTERED = true>
+__device__ __forceinline__ bool exchange_fold(const FoldArgs &a, const FoldCtx &ctx, cg::cluster_group &cluster,
+                                              int csize, int c_lo, int c_hi, int b_lo, int nb, bool writer,
+                                              __half *x_s, int refill_w, int refill_n, FoldRegs<ITEMS> &fr,
+                                              float *red, float *st, float *stf, int *failed_s) {
   const int tid = threadIdx.x;
   const int nseg = c_hi - c_lo;
   const int d = a.d;
   if (tid == 0) *failed_s = 0;
-  const int slot = exchange_slot(a.ctl, a.seq);
-  // once a wait has run out the exchange is dead: later calls do not wait again
-  const bool dead = a.ctl[1] != 0u;
-  char *local = static_cast<char *>(a.bufs[a.rank]);
+  const int slot = ctx.slot;
+  const bool dead = ctx.dead;
+  char *local = ctx.local;
   const size_t cur_off = (size_t)slot * a.world * a.slot_bytes;
   __syncthreads();
 
@@ -178,9 +196,27 @@ __device__ __forceinline__ bool exchange_fold(const FoldArgs &a, cg::cluster_gro
     for (size_t c = lo + tid; c < hi; c += THREADS) old[c] = s;
   }
 
-  // 3. wait for the chunks of every piece, reduce in rank order, residual add
+  // 3. wait for the chunks of every piece, reduce in rank order, residual add. With few chunks per thread the
+  //    loads of ALL of them are issued before any is looked at (one round trip instead of one per chunk).
   const unsigned long long t_start = global_timer_ns();
   bool gave_up = dead;
+  constexpr bool BATCHED = ITEMS <= 2;
+  uint4 vb[BATCHED ? ITEMS : 1][AR_MAX_WORLD];
+  uint4 rb[BATCHED ? ITEMS : 1];
+  if (BATCHED && !gave_up) {
+#pragma unroll
+    for (int it = 0; it < (BATCHED ? ITEMS : 1); ++it) {
+      DJV_FOLD_ITEM(it);
+      if (valid) {
+        const size_t elem = (size_t)row * d + (size_t)ch * 8;
+        rb[it] = a.residual ? *reinterpret_cast<const uint4 *>(a.residual + elem) : make_uint4(0, 0, 0, 0);
+        const char *piece0 = local + cur_off + elem * 2;
+#pragma unroll
+        for (int p = 0; p < AR_MAX_WORLD; ++p)
+          if (p < a.world) vb[it][p] = ld_sys16(piece0 + (size_t)p * a.slot_bytes);
+      }
+    }
+  }
 #pragma unroll
   for (int it = 0; it < ITEMS; ++it) {
     DJV_FOLD_ITEM(it);
@@ -189,12 +225,24 @@ __device__ __forceinline__ bool exchange_fold(const FoldArgs &a, cg::cluster_gro
     for (int e = 0; e < 8; ++e) f[e] = 0.f;
     if (valid && !gave_up) {
       const size_t elem = (size_t)row * d + (size_t)ch * 8;
-      // the residual chunk is requested before the wait on the peers, not after it
-      const uint4 rres = a.residual ? *reinterpret_cast<const uint4 *>(a.residual + elem) : make_uint4(0, 0, 0, 0);
       const char *piece0 = local + cur_off + elem * 2;
       uint4 v[AR_MAX_WORLD];
+      uint4 rres;
       unsigned missing = (1u << a.world) - 1u;
-      // all pieces are requested together; only the ones not there yet are asked for again
+      if (BATCHED) {
+        rres = rb[BATCHED ? it : 0];
+#pragma unroll
+        for (int p = 0; p < AR_MAX_WORLD; ++p) {
+          if (p < a.world) {
+            v[p] = vb[BATCHED ? it : 0][p];
+            if (arrived16(v[p])) missing &= ~(1u << p);
+          }
+        }
+      } else {
+        // the residual chunk is requested before the wait on the peers, not after it
+        rres = a.residual ? *reinterpret_cast<const uint4 *>(a.residual + elem) : make_uint4(0, 0, 0, 0);
+      }
+      // all missing pieces are requested together; only the ones not there yet are asked for again
       while (missing != 0u) {
 #pragma unroll
         for (int p = 0; p < AR_MAX_WORLD; ++p)
@@ -240,55 +288,88 @@ __device__ __forceinline__ bool exchange_fold(const FoldArgs &a, cg::cluster_gro
   if (failed && tid == 0 && !dead) atomicExch(&a.ctl[1], (unsigned)DJV_ERR_TIMEOUT);
   if (a.gamma == nullptr) return !failed;
 
-  // 4. LayerNorm statistics: per block sum and centred second moment, merged over the cluster
-  const float n_loc = (float)(nseg * 8);
-  for (int b = 0; b < nb; ++b) {
-    float s = 0.f;
+  // 4. LayerNorm statistics: every warp takes the sum and the centred second moment of its own values (two
+  //    passes over registers, shuffles only); the warps' and then the blocks' moments are merged exactly
+  //    (groups g with n_g, sum_g, M2_g: M2 = sum_g M2_g + sum_g n_g (mean_g - mean)^2).
+  //    red: [THREADS / 32][nb][3] floats.
+  {
+    const int lane = tid % WARP, warp = tid / WARP;
+    for (int b = 0; b < nb; ++b) {
+      float s = 0.f, cnt = 0.f;
 #pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-      DJV_FOLD_ITEM(it);
-      if (valid && row - b_lo == b) {
+      for (int it = 0; it < ITEMS; ++it) {
+        DJV_FOLD_ITEM(it);
+        if (valid && row - b_lo == b) {
+          cnt += 8.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s += fr.vals[it][e];
+          for (int e = 0; e < 8; ++e) s += fr.vals[it][e];
+        }
+      }
+      s = warp_sum(s);
+      cnt = warp_sum(cnt);
+      const float mean_w = cnt > 0.f ? s / cnt : 0.f;
+      float q = 0.f;
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        DJV_FOLD_ITEM(it);
+        if (valid && row - b_lo == b) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float t = fr.vals[it][e] - mean_w;
+            q += t * t;
+          }
+        }
+      }
+      q = warp_sum(q);
+      if (lane == 0) {
+        red[(warp * nb + b) * 3 + 0] = cnt;
+        red[(warp * nb + b) * 3 + 1] = s;
+        red[(warp * nb + b) * 3 + 2] = q;
       }
     }
-    s = block_sum_t<THREADS>(s, red);
-    const float mean_loc = nseg > 0 ? s / n_loc : 0.f;
-    float q = 0.f;
-#pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-      DJV_FOLD_ITEM(it);
-      if (valid && row - b_lo == b) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float t = fr.vals[it][e] - mean_loc;
-          q += t * t;
+    __syncthreads();
+    // warps -> block: warp 0, lane w takes warp w's moments; all groups are merged at once
+    // (M2 = sum of the groups' M2 + sum of n_g * (mean_g - mean)^2), so the order of the shuffles is the only
+    // order there is, and it is the same in every block.
+    if (tid < WARP) {
+      for (int b = 0; b < nb; ++b) {
+        float nw = 0.f, sw = 0.f, qw = 0.f;
+        if (tid < THREADS / WARP) {
+          nw = red[(tid * nb + b) * 3 + 0];
+          sw = red[(tid * nb + b) * 3 + 1];
+          qw = red[(tid * nb + b) * 3 + 2];
+        }
+        const float n = warp_sum(nw), sum = warp_sum(sw);
+        const float mean = n > 0.f ? sum / n : 0.f;
+        const float dm = nw > 0.f ? sw / nw - mean : 0.f;
+        const float M2 = warp_sum(qw + nw * dm * dm);
+        if (tid == 0) {
+          st[b * 4 + 0] = sum;
+          st[b * 4 + 1] = M2;
+          st[b * 4 + 2] = n;
         }
       }
     }
-    q = block_sum_t<THREADS>(q, red);
-    if (tid == 0) {
-      st[b * 4 + 0] = s;
-      st[b * 4 + 1] = q;
-      st[b * 4 + 2] = n_loc;
-    }
   }
-  cluster.sync();
-  if (tid < nb) {
-    float S = 0.f;
-    for (int j = 0; j < csize; ++j) S += cluster.map_shared_rank(st, j)[tid * 4 + 0];
-    const float mean = S / (float)d;
-    float M2 = 0.f;
-    for (int j = 0; j < csize; ++j) {
-      const float *r = cluster.map_shared_rank(st, j);
-      const float sj = r[tid * 4 + 0], qj = r[tid * 4 + 1], nj = r[tid * 4 + 2];
-      if (nj > 0.f) {
-        const float dm = sj / nj - mean;
-        M2 += qj + nj * dm * dm;
+  if (CLUSTERED) cluster.sync(); else __syncthreads();
+  // blocks -> row: lane j takes block j's moments (one round of remote reads), merged the same way
+  if (tid < WARP) {
+    for (int b = 0; b < nb; ++b) {
+      float nj = 0.f, sj = 0.f, qj = 0.f;
+      if (tid < csize) {
+        const float *r = CLUSTERED ? cluster.map_shared_rank(st, tid) : st;
+        sj = r[b * 4 + 0];
+        qj = r[b * 4 + 1];
+        nj = r[b * 4 + 2];
+      }
+      const float mean = warp_sum(sj) / (float)d;
+      const float dm = nj > 0.f ? sj / nj - mean : 0.f;
+      const float M2 = warp_sum(qj + nj * dm * dm);
+      if (tid == 0) {
+        stf[b * 2 + 0] = mean;
+        stf[b * 2 + 1] = rsqrtf(M2 / (float)d + a.eps);
       }
     }
-    stf[tid * 2 + 0] = mean;
-    stf[tid * 2 + 1] = rsqrtf(M2 / (float)d + a.eps);
   }
   __syncthreads();
   if (failed) return false;

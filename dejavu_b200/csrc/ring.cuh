@@ -37,12 +37,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
   return ok != 0;
 }
 // Bounded wait for phase `parity` of the barrier. A copy from this GPU's own memory always completes, so the
-// limit is never reached in a healthy run; it exists so that no spin in this library is unbounded. Returns
-// false when it ran out (each try_wait itself blocks for a hardware-defined time before it reports failure).
+// limit (one second of %globaltimer) is never reached in a healthy run; it exists so that no spin in this
+// library is unbounded. Returns false when it ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
-  for (int i = 0; i < (1 << 22); ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (t - t0 > 1000ull * 1000 * 1000) return false;
+  }
 }
 // global -> this block's shared memory, `bytes` a multiple of 16, both addresses 16-byte aligned
 __device__ __forceinline__ void bulk_load(void *smem_dst, const void *gmem_src, unsigned bytes, uint64_t *bar) {

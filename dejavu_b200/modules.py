@@ -50,6 +50,11 @@ FUSED_MLP = os.environ.get("DJV_FUSED_MLP", "1") != "0"
 # kernel (the fused MLP kernel then follows out_proj with a single programmatic edge and streams its weights while
 # out_proj runs), "mlp" = right before the MLP (development knob)
 MLP_IDX_JOIN = os.environ.get("DJV_MLP_IDX_JOIN", "attend")
+# L2 warm-up of the rows an index list names, as soon as the list exists: "0" off (default: measured slower, the
+# extra traffic lengthens the memory latency every kernel of the main chain is bound by), "1" on, "auto" = on when
+# the weights a rank gathers per layer stay below DJV_L2_PREFETCH_MB (development knob)
+L2_PREFETCH = os.environ.get("DJV_L2_PREFETCH", "0")
+L2_PREFETCH_MB = float(os.environ.get("DJV_L2_PREFETCH_MB", "100"))
 _SIDE_STREAMS: dict = {}
 _SIDE_DIRTY: dict = {}  # device index -> names of side streams forked since the last join
 
@@ -363,6 +368,17 @@ class ParallelMHASparseAttMlp(nn.Module):
     def link_next(self, mixer):
         self.__dict__["next_mixer"] = mixer
 
+    mlp_ref = None  # the MLP of the same block (set by the block; not a submodule)
+
+    def l2_prefetch_enabled(self) -> bool:
+        """Whether index lists are followed by an L2 warm-up of the rows they name."""
+        if L2_PREFETCH in ("0", "1"):
+            return L2_PREFETCH == "1"
+        d, hd = self.embed_dim, self.head_dim
+        a = self.att_k if (self.sparse_attention and self.att_k) else self.num_head_per_node
+        k = self.mlp_k if self.mlp_k else (self.mlp_ref.fc1.weight.shape[0] if self.mlp_ref is not None else 0)
+        return (4 * a * hd * d * 2 + 2 * k * d * 2) <= L2_PREFETCH_MB * 1e6
+
     def __init__(self, embed_dim, num_heads, process_group, sp_kwargs, bias=True, dropout=0.0,
                  softmax_scale=None, causal=False, layer_idx=None, rotary_emb_dim=0, rotary_emb_scale_base=0,
                  use_flash_attn=False, checkpointing=False, sequence_parallel=True, device=None,
@@ -497,6 +513,9 @@ class ParallelMHASparseAttMlp(nn.Module):
             with _side(x, "mlp", after=mlp_sp_logit) as done:
                 mlp_idx = ops.topk_indices(mlp_sp_logit, self.mlp_k, torch.int32)
                 done(mlp_idx)
+                if decoding and self.mlp_ref is not None and x.is_cuda and self.l2_prefetch_enabled():
+                    # the rows this layer's MLP is going to gather, a good part of a layer ahead of it
+                    ops.prefetch_rows_l2(mlp_idx, self.mlp_ref.fc1.weight, self.mlp_ref.fc2.weight_t)
         result = {"att_idx": None}
 
         def predict_heads():
@@ -515,6 +534,12 @@ class ParallelMHASparseAttMlp(nn.Module):
                         idx = ops.topk_indices(scores, self.att_k, torch.int32)
                     result["att_idx"] = idx
                     done(idx)
+                    if nxt is not None and nxt.sparse_attention and self.l2_prefetch_enabled():
+                        # the next layer's q, k, v slabs and out_proj columns of the heads just selected
+                        n_n, hd_n = nxt.num_head_per_node, nxt.head_dim
+                        wq = nxt.Wqkv.weight.view(3, n_n * hd_n, nxt.embed_dim)
+                        ops.prefetch_rows_l2(idx, wq[0], wq[1], wq[2], rows_per_index=hd_n)
+                        ops.prefetch_head_columns_l2(idx, nxt.out_proj.weight, hd_n)
 
         if decoding:
             assert do_token_generation
@@ -576,6 +601,7 @@ class BlockMlpAttSparse(nn.Module):
         self.mlp = mlp_cls(dim)
         self.norm2 = norm_cls(dim)
         # per-rank budgets (block_dejavu.py:549-553)
+        self.mixer.__dict__["mlp_ref"] = self.mlp
         if hasattr(self.mlp, "sp"):
             self.mixer.mlp_k = self.mlp.sp.K
         if getattr(self.mixer, "sp", None) is not None:

@@ -10,6 +10,7 @@ There is no CPU path: tensors must live on a CUDA device.
 from __future__ import annotations
 
 import contextlib
+import os
 
 from typing import Optional
 
@@ -19,6 +20,7 @@ from . import _lib
 from ._lib import call
 
 _ACTIVATIONS = ["id", "relu", "gelu", "gelu_approx", "squared_relu"]
+
 _scratch_cache: dict = {}
 
 
@@ -196,8 +198,8 @@ def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None, push_comm=None):
     need = _lib.load().djv_mlp_sparse_fused_scratch_bytes(batch, N, M)
     scratch = _scratch(need, x.device)
     call("djv_mlp_sparse_fused", output.data_ptr(), W1.data_ptr(), W2t.data_ptr(), x.data_ptr(), idx.data_ptr(),
-         _ptr(bias1), _ptr(bias2), batch, N, M, W1.stride(0), W2t.stride(0), idx64, scratch.data_ptr(),
-         scratch.numel(), _stream())
+         _ptr(bias1), _ptr(bias2), batch, N, M, W1.shape[0], W1.stride(0), W2t.stride(0), idx64,
+         scratch.data_ptr(), scratch.numel(), _stream())
     return output
 
 
@@ -222,8 +224,8 @@ def mlp_sparse_after_exchange(comm, partial, residual, norm_weight, norm_bias, e
     call("djv_mlp_sparse_fused_exchange", comm.handle, seq_in, _lib.EXCHANGE_REFILL, seq_out,
          None if push else out.data_ptr(), r.data_ptr(), _ptr(None if residual is None else residual.contiguous()),
          norm_weight.data_ptr(), norm_bias.data_ptr(), float(eps), W1.data_ptr(), W2t.data_ptr(), idx.data_ptr(),
-         _ptr(bias1), _ptr(bias2), batch, N, M, W1.stride(0), W2t.stride(0), idx64, scratch.data_ptr(),
-         scratch.numel(), _stream())
+         _ptr(bias1), _ptr(bias2), batch, N, M, W1.shape[0], W1.stride(0), W2t.stride(0), idx64,
+         scratch.data_ptr(), scratch.numel(), _stream())
     if push:
         comm.note_pushed(out, seq_out)
     return out, r
@@ -339,6 +341,33 @@ def k_cache_copy_sparse(k, k_cache, head_idx, seqlen_idx, padding=None) -> None:
     _, _, _, seqlen, _ = k_cache.shape
     assert k_cache.shape == (1, nheads, head_dim // 8, seqlen, 8)
     _cache_copy("djv_k_cache_copy_sparse", k, k_cache, head_idx, seqlen_idx, padding, seqlen, head_dim)
+
+
+# ---- L2 warm-up (hints; no counterpart in the reference) ---------------------------------------------
+
+def prefetch_rows_l2(idx: torch.Tensor, *weights: torch.Tensor, rows_per_index: int = 1):
+    """Ask for rows idx[m] of up to three (Z, N) matrices to be brought into L2. With rows_per_index = r an index
+    names r consecutive rows (a head's slab of a (heads * r, N) matrix)."""
+    assert 1 <= len(weights) <= 3
+    w0 = weights[0]
+    _require_cuda(idx, *weights)
+    for w in weights:
+        assert w.dtype == torch.float16 and w.stride(1) == 1 and w.shape == w0.shape and w.stride(0) == w0.stride(0)
+    assert rows_per_index == 1 or w0.stride(0) == w0.shape[1], "a slab of several rows must be contiguous"
+    idx, idx64 = _idx_args(idx)
+    ptrs = [w.data_ptr() for w in weights] + [None] * (3 - len(weights))
+    call("djv_prefetch_rows_l2", ptrs[0], ptrs[1], ptrs[2], idx.data_ptr(), idx64, idx.numel(),
+         w0.shape[0] // rows_per_index, w0.stride(0) * 2 * rows_per_index, w0.shape[1] * 2 * rows_per_index,
+         _stream())
+
+
+def prefetch_head_columns_l2(head_idx: torch.Tensor, weight: torch.Tensor, head_dim: int):
+    """Ask for the columns of a (rows, heads * head_dim) matrix that belong to the listed heads (int32)."""
+    _require_cuda(head_idx, weight)
+    assert head_idx.dtype == torch.int32 and weight.dtype == torch.float16 and weight.stride(1) == 1
+    assert (head_dim * 2) % 128 == 0
+    call("djv_prefetch_segments_l2", weight.data_ptr(), head_idx.contiguous().data_ptr(), head_idx.numel(),
+         weight.shape[1] // head_dim, weight.shape[0], weight.stride(0) * 2, head_dim * 2, _stream())
 
 
 # ---- operators the reference obtains from torch / third-party extensions -------------------------

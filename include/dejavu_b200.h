@@ -48,13 +48,33 @@ const char *djv_status_string(int status);
 /* Number of kernels launched by this library on this process since load (all threads). */
 unsigned long long djv_launch_count(void);
 /* Per calling thread, default 0. While set, the gather / head-sparse kernels launched by this thread read
- * their index list (idx, head_idx, the attention state) and prefetch the first weight rows into L2 BEFORE
- * they wait for the kernel launched just before them on the stream (they are launched with programmatic
- * dependent launch and would otherwise idle until it has drained). The caller thereby promises that those
- * index arguments are complete before the launch can start: produced on another stream and joined with an
- * event, or by earlier work ordered by a full (non-programmatic) dependency. Activations are still read
- * after the wait. Kernels without an index list (idx == NULL) always prefetch. No reference counterpart. */
+ * their index list (idx, head_idx, the attention state) and start fetching weight rows BEFORE they wait for the
+ * kernel launched just before them on the stream (they are launched with programmatic dependent launch and
+ * would otherwise idle until it has drained). It is a hint that the index arguments are already complete at
+ * that point (produced on another stream and joined with an event some kernels earlier); it never changes a
+ * result: the prefetching kernels only issue L2 prefetches from what they find, and the one-pass sparse MLP
+ * kernel, which starts real copies, re-reads the list after the wait and starts over if it changed (and only
+ * takes the hint when it is given the row count to bound the values, see djv_mlp_sparse_fused). Note that an
+ * event wait in front of a programmatically launched kernel does not by itself order that kernel's pre-wait
+ * reads after the event: inside a captured CUDA graph such an edge can be programmatic as well. Activations are
+ * always read after the wait. Kernels without an index list (idx == NULL) always prefetch. No reference
+ * counterpart. */
 void djv_set_early_weight_prefetch(int enabled);
+
+/* ---------------------------------------------------------------------------------------------
+ * L2 warm-up for short index lists (no counterpart in the reference). When the rows a rank reads per layer fit
+ * the L2 cache, the kernels of the decode step are bound by memory latency; these calls ask, as soon as an
+ * index list exists, for the rows it names to be brought into L2 (bulk prefetches issued by a tiny kernel), so
+ * that the consumers find them there. Pure hints: no result depends on them; indices outside [0, Z) are skipped.
+ *   djv_prefetch_rows_l2: rows idx[0..M) of up to three matrices sharing the list (NULL = absent), a row being
+ *     row_bytes contiguous bytes at base + idx[m] * ld_bytes (fc1 / fc2^T rows; the q, k, v slabs of a head).
+ *   djv_prefetch_segments_l2: for every row n < nrows of w the seg_bytes at n * ld_bytes + idx[i] * seg_bytes
+ *     (the columns of out_proj.weight that belong to the listed heads). idx int32.
+ * ------------------------------------------------------------------------------------------- */
+int djv_prefetch_rows_l2(const void *w0, const void *w1, const void *w2, const void *idx, int idx_is_64, int M,
+                         int Z, long long ld_bytes, long long row_bytes, void *stream);
+int djv_prefetch_segments_l2(const void *w, const int32_t *idx, int M, int Z, int nrows, long long ld_bytes,
+                             int seg_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Gather GEMV (fc1):  y[b,m] = act( sum_n w[idx[m],n] * x[b,n] + bias[idx[m]] ),  b<B, m<M.
@@ -118,14 +138,21 @@ int djv_mlp_sparse(void *y, void *h, const void *w1, const void *w2t, const void
  * (djv_mlp_sparse_fused_supported says whether a shape qualifies; use djv_mlp_sparse otherwise).
  *   scratch: djv_mlp_sparse_fused_scratch_bytes(B,N,M) bytes, 256-byte aligned, first 4096 bytes ZERO before
  *   the first call (left zero again); calls that share scratch must not overlap on the GPU.
+ * Z: number of rows of w1 / w2t, or 0. With Z > 0 the kernel checks every index value it uses: a value outside
+ * [0, Z) is counted (djv_mlp_ring_bad_indices) and row 0 is read in its place, instead of an access outside the
+ * matrices. With Z = 0 index values are not checked, as in the kernels this replaces. Only with Z > 0 does the
+ * kernel honour djv_set_early_weight_prefetch: it then starts its weight copies from the index list as it finds
+ * it before its predecessor has finished, reads the list again afterwards and starts the copies anew should
+ * any entry have changed, so the hint can never change a result.
  * djv_mlp_ring_timeouts(): how many bounded waits on the kernel's own asynchronous copies ever ran out in
  * this process (0 in a healthy run; synchronises).
  * ------------------------------------------------------------------------------------------- */
 int djv_mlp_sparse_fused_supported(int B, int N, int M);
 size_t djv_mlp_sparse_fused_scratch_bytes(int B, int N, int M);
 unsigned djv_mlp_ring_timeouts(void);
+unsigned djv_mlp_ring_bad_indices(void);
 int djv_mlp_sparse_fused(void *y, const void *w1, const void *w2t, const void *x, const void *idx,
-                         const void *bias1, const void *bias2, int B, int N, int M, long long ldw1,
+                         const void *bias1, const void *bias2, int B, int N, int M, int Z, long long ldw1,
                          long long ldw2t, int idx_is_64, void *scratch, size_t scratch_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
@@ -331,7 +358,7 @@ int djv_allreduce_add_layernorm(djv_comm *comm, int seq, int flags, void *y, voi
 int djv_mlp_sparse_fused_exchange(djv_comm *comm, int seq_in, int flags, int seq_out, void *y, void *r_out,
                                   const void *residual, const void *gamma, const void *beta, float eps,
                                   const void *w1, const void *w2t, const void *idx, const void *bias1,
-                                  const void *bias2, int B, int N, int M, long long ldw1, long long ldw2t,
+                                  const void *bias2, int B, int N, int M, int Z, long long ldw1, long long ldw2t,
                                   int idx_is_64, void *scratch, size_t scratch_bytes, void *stream);
 
 #ifdef __cplusplus

@@ -175,7 +175,7 @@ def test_fused_mlp_behind_the_exchange_single_gpu(cuda, world, Z, N, M, B):
         resd = res.to(cuda)
         _lib.call("djv_mlp_sparse_fused_exchange", comm, seq_in, _lib.EXCHANGE_REFILL, seq_out, None, r.data_ptr(),
                   resd.data_ptr(), dg.data_ptr(), dbt.data_ptr(), 1e-5, dW1.data_ptr(), dW2t.data_ptr(),
-                  didx.data_ptr(), db1.data_ptr(), db2.data_ptr(), B, N, M, N, N, 0, scratch.data_ptr(), need, st)
+                  didx.data_ptr(), db1.data_ptr(), db2.data_ptr(), B, N, M, Z, N, N, 0, scratch.data_ptr(), need, st)
         assert lib.djv_comm_status(comm) == 0
         acc = torch.zeros(B, d)
         for p in range(world):
@@ -196,7 +196,7 @@ def test_fused_mlp_behind_the_exchange_single_gpu(cuda, world, Z, N, M, B):
             own[slot_in, p, :B * d] = _no_neg_zero(parts[p]).reshape(-1).view(torch.int16).to(cuda)
         _lib.call("djv_mlp_sparse_fused_exchange", comm, seq_in, 0, -1, y.data_ptr(), None, resd.data_ptr(),
                   dg.data_ptr(), dbt.data_ptr(), 1e-5, dW1.data_ptr(), dW2t.data_ptr(), didx.data_ptr(),
-                  db1.data_ptr(), db2.data_ptr(), B, N, M, N, N, 0, scratch.data_ptr(), need, st)
+                  db1.data_ptr(), db2.data_ptr(), B, N, M, Z, N, N, 0, scratch.data_ptr(), need, st)
         assert torch.equal(_no_neg_zero(y.cpu()).view(-1), sent[0])
         _lib.call("djv_comm_end_step", comm, 2, st)
         # the consumer of exchange seq_out would recycle slot_in + 3; do it by hand so that slots stay clean
@@ -226,7 +226,7 @@ def test_fused_mlp_wait_on_a_missing_peer_runs_out(cuda):
     r = torch.zeros(B, N, dtype=torch.float16, device=cuda)
     _lib.call("djv_mlp_sparse_fused_exchange", comm, 0, _lib.EXCHANGE_REFILL, 1, None, r.data_ptr(), None,
               g.data_ptr(), bt.data_ptr(), 1e-5, W1.data_ptr(), W2t.data_ptr(), idx.data_ptr(), b1.data_ptr(),
-              b2.data_ptr(), B, N, M, N, N, 0, scratch.data_ptr(), need, torch.cuda.current_stream().cuda_stream)
+              b2.data_ptr(), B, N, M, Z, N, N, 0, scratch.data_ptr(), need, torch.cuda.current_stream().cuda_stream)
     assert lib.djv_comm_status(comm) == _lib.ERR_TIMEOUT
     own = bufs_t[0].view(SLOTS, 2, N)
     assert bool((own[1, 0] == SENT_I16).all()), "nothing was sent"
