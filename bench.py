@@ -162,7 +162,7 @@ def kernel_rooflines(model, cfg, world, peak, comm=None):
     rec("gather_gemv_fc2", us, K * d * 2 + K * 2 + d * 2 + d * 2)
     if _lib.load().djv_mlp_sparse_fused_supported(1, d, K):
         us = kernel_timing([lambda l=l, i=i: ops.mlp_sparse(x, l.mlp.fc1.weight, l.mlp.fc2.weight_t, i, l.mlp.fc1.bias,
-                                                            l.mlp.fc2.bias) for l, i in zip(layers, idxs)])
+                                                            l.mlp.fc2.bias, fused=True) for l, i in zip(layers, idxs)])
         rec("mlp_sparse_fused", us, 2 * K * d * 2 + K * 2 + K * 4 + d * 2 + 2 * d * 2)
     norm = layers[0].norm1
     us = kernel_timing([lambda: ops.add_layernorm(x, x, norm.weight, norm.bias, norm.eps) for _ in layers])
@@ -236,17 +236,52 @@ def exchange_check(model, cfg, comm, dev, world, pg, steps=16, prompt_len=24):
             logits.append(out)
         return toks, logits
 
-    with torch.inference_mode():
-        model.transformer.enable_fused_allreduce(None)
-        toks, ref = run(None)
-        model.transformer.enable_fused_allreduce(comm)
-        _, got = run(toks)
-        model.transformer.enable_fused_allreduce(None)
-        torch.cuda.synchronize()
-    max_diff, decisive, agree = 0.0, 0, 0
+    # Index selection is discontinuous (a near-tie in a predictor's scores picks different neurons or heads, and a
+    # randomly initialised deep network amplifies that), so parity is defined given identical predictor scores:
+    # the scores the plain run fed to its top-K kernels are recorded and fed to the same kernels of the second run.
+    from dejavu_b200 import ops
+
+    real_topk, real_open = ops.topk_indices, ops.topk_indices_open_step
+    tape, cursor = [], [0]
+
+    def rec_topk(scores, *a, **k):
+        tape.append(scores.clone())
+        return real_topk(scores, *a, **k)
+
+    def rec_open(scores, *a, **k):
+        tape.append(scores.clone())
+        return real_open(scores, *a, **k)
+
+    def play_topk(scores, *a, **k):
+        out = real_topk(tape[cursor[0]], *a, **k)
+        cursor[0] += 1
+        return out
+
+    def play_open(scores, *a, **k):
+        out = real_open(tape[cursor[0]], *a, **k)
+        cursor[0] += 1
+        return out
+
+    try:
+        with torch.inference_mode():
+            model.transformer.enable_fused_allreduce(None)
+            ops.topk_indices, ops.topk_indices_open_step = rec_topk, rec_open
+            toks, ref = run(None)
+            model.transformer.enable_fused_allreduce(comm, fused_mlp="1")
+            ops.topk_indices, ops.topk_indices_open_step = play_topk, play_open
+            _, got = run(toks)
+            model.transformer.enable_fused_allreduce(None)
+            torch.cuda.synchronize()
+    finally:
+        ops.topk_indices, ops.topk_indices_open_step = real_topk, real_open
+    assert cursor[0] == len(tape), "the two runs made different numbers of selections"
+    # fp16 rounding of two different summation orders, carried through n_layer residual blocks: the bound scales
+    # with the size of the logits (3 % of the largest one, plus a small absolute part)
+    max_diff, decisive, agree, within = 0.0, 0, 0, True
     for a, b in zip(ref[1:], got[1:]):
         diff = float((a - b).abs().max())
         max_diff = max(max_diff, diff)
+        within = within and diff <= 2e-2 + 3e-2 * float(a.abs().max())
         top2 = a.topk(2).values
         if float(top2[0] - top2[1]) > 4 * max(diff, 1e-3):
             decisive += 1
@@ -254,9 +289,11 @@ def exchange_check(model, cfg, comm, dev, world, pg, steps=16, prompt_len=24):
     status = comm.status()
     decode_status = max(abs(l.mixer.decode_status()) for l in model.transformer.layers)
     result = {"steps": steps, "plain_path": "nccl all_reduce" if world > 1 else "stand-alone kernels",
+              "selections": "predictor scores of the plain run replayed (%d top-K calls)" % len(tape),
               "tokens_equal": agree == decisive, "decisive_steps": decisive,
               "max_abs_logit_diff": round(max_diff, 5), "comm_status": status, "decode_status": decode_status}
-    flags = torch.tensor([int(result["tokens_equal"]), int(max_diff < 5e-2), int(status == 0)], device=dev)
+    result["logits_within_tolerance"] = within
+    flags = torch.tensor([int(result["tokens_equal"]), int(within), int(status == 0)], device=dev)
     if world > 1:
         import torch.distributed as dist
 
@@ -396,11 +433,13 @@ def main():
     if args.fused_allreduce:
         from dejavu_b200.comm import TensorParallelComm
 
-        # world 1: a one-rank exchange object, so that the same kernels run (producers that send, exchange +
-        # LayerNorm, the one-launch second half of a block)
         comm = TensorParallelComm(pg, dev, max_bytes=cfg.hidden_size * 2)
         check = exchange_check(model, cfg, comm, dev, world, pg)
-        model.transformer.enable_fused_allreduce(comm)
+        if world > 1:
+            model.transformer.enable_fused_allreduce(comm)
+        # One rank: the exchange kernels (producers that send, exchange + LayerNorm, the one-launch second half of a
+        # block) run for the check above and for the kernel timings below, through a one-rank exchange object; the
+        # timed decode path hands tensors from kernel to kernel directly, which is faster without peers.
     torch.cuda.synchronize()
     t_build = time.time() - t_build
 

@@ -68,6 +68,7 @@ SIGNATURES = {
     "djv_prefetch_rows_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp]),
     "djv_prefetch_segments_l2": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _vp]),
     "djv_mlp_sparse_fused_supported": (_i, [_i, _i, _i]),
+    "djv_mlp_sparse_fused_single_batch": (_i, [_i, _i, _i]),
     "djv_mlp_sparse_fused_scratch_bytes": (_sz, [_i, _i, _i]),
     "djv_mlp_ring_timeouts": (C.c_uint, []),
     "djv_mlp_ring_bad_indices": (C.c_uint, []),

@@ -700,6 +700,24 @@ extern "C" int djv_mlp_sparse_fused_supported(int B, int N, int M) {
   return B >= 1 && B <= MR_MAX_B && N >= 64 && N % (8 * 8) == 0 && N / (8 * 8) <= MR_THREADS && M >= 1;
 }
 
+// 1 when the plan keeps every row of a cluster in flight at once (one exchange of partial dots per cluster): the
+// regime of short index lists the one-pass kernel is made for. Needs a CUDA device (occupancy query).
+extern "C" int djv_mlp_sparse_fused_single_batch(int B, int N, int M) {
+  if (!djv_mlp_sparse_fused_supported(B, N, M)) return 0;
+  const int C = 8;
+  const size_t stage = (size_t)2 * (N / C) * 2;
+  const size_t fixed = ring_fixed_bytes(B, N, 0, C);
+  int stages_max = (int)((MR_SMEM_BUDGET - fixed) / stage);
+  if (stages_max > MR_MAX_STAGES) stages_max = MR_MAX_STAGES;
+  if (stages_max < 2) return 0;
+  int maxcl = sm_count() / C * 7 / 8;  // what the cluster granularity of a GPC leaves (15 on a 148-SM part)
+  if (maxcl > MR_MAX_CLUSTERS) maxcl = MR_MAX_CLUSTERS;
+  if (maxcl < 1) maxcl = 1;
+  int n_cl = ceil_div(M, 4);
+  if (n_cl > maxcl) n_cl = maxcl;
+  return ceil_div(M, n_cl) <= stages_max ? 1 : 0;
+}
+
 extern "C" size_t djv_mlp_sparse_fused_scratch_bytes(int B, int N, int M) {
   if (B < 1 || N < 8 || M < 0) return 0;
   return MR_COUNTER_BYTES + (size_t)MR_MAX_CLUSTERS * B * N * sizeof(float);

@@ -168,11 +168,14 @@ class GPTModel(nn.Module):
         self.mlp_sparse = getattr(config, "mlp_sparse", False)
         self.comm = None
 
-    def enable_fused_allreduce(self, comm):
-        """Route every TP all-reduce of the decode step through the one-shot all-reduce + add + LayerNorm."""
+    def enable_fused_allreduce(self, comm, fused_mlp=None):
+        """Route every TP all-reduce of the decode step through the one-shot all-reduce + add + LayerNorm.
+        fused_mlp: "1" / "0" / "auto" = whether the second half of a block (exchange, residual, norm2, sparse MLP,
+        send) runs as one kernel; None keeps the process-wide default (DJV_FUSED_MLP)."""
         self.comm = comm
         for layer in self.layers:
             layer.enable_fused_allreduce(comm)
+            layer.mlp.fused_mlp = fused_mlp
 
     def set_dense(self, dense: bool, cublas: bool = True):
         """Dense comparator mode on the SAME weights: every head and every neuron, no predictors (what

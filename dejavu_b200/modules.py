@@ -44,8 +44,9 @@ FUSE_STEP_OPEN = os.environ.get("DJV_FUSE_STEP_OPEN", "1") != "0"
 PUSH_PARTIALS = os.environ.get("DJV_PUSH_PARTIALS", "1") != "0"
 # kernels whose index list is known to be complete prefetch weights before their PDL wait (development knob)
 EARLY_PREFETCH = os.environ.get("DJV_EARLY_PREFETCH", "1") != "0"
-# with a comm: exchange + residual + LayerNorm + fc1 + ReLU + fc2 (+ send) of a block in one kernel (development knob)
-FUSED_MLP = os.environ.get("DJV_FUSED_MLP", "1") != "0"
+# with a comm: exchange + residual + LayerNorm + fc1 + ReLU + fc2 (+ send) of a block in one kernel. "auto": for a
+# real tensor-parallel group when the shard's index list is short enough to be in flight at once; "1" / "0" force
+FUSED_MLP = os.environ.get("DJV_FUSED_MLP", "auto")
 # where the main stream joins the side stream that selects this layer's MLP rows: "attend" = before the attention
 # kernel (the fused MLP kernel then follows out_proj with a single programmatic edge and streams its weights while
 # out_proj runs), "mlp" = right before the MLP (development knob)
@@ -245,6 +246,7 @@ class ParallelFusedMLPDejavu(nn.Module):
     run_predictor = True         # False: dense comparator mode, skip the look-ahead predictor
     dense_decode_cublas = False  # True: dense decode GEMVs through torch (cuBLAS)
     push_comm = None             # TensorParallelComm: fc2 sends its result to the peers itself
+    fused_mlp = None             # "0" / "1" / "auto" for this module, None = the process-wide DJV_FUSED_MLP
 
     def __init__(self, in_features, hidden_features, sp_kwargs, out_features=None, activation="gelu_approx",
                  layer_idx=None, process_group=None, bias1=True, bias2=True, sequence_parallel=True,
@@ -302,14 +304,24 @@ class ParallelFusedMLPDejavu(nn.Module):
         return out, mlp_logit
 
 
+    def fuses_after_exchange(self, batch: int, d: int, rows: int) -> bool:
+        """Whether the second half of the block runs as one kernel for this shape (see FUSED_MLP)."""
+        mode = self.fused_mlp if self.fused_mlp is not None else FUSED_MLP
+        if mode == "0" or self.push_comm is None or self.activation != "relu":
+            return False
+        lib = _lib.load()
+        if mode == "1":
+            return bool(lib.djv_mlp_sparse_fused_supported(batch, d, rows))
+        return self.push_comm.world > 1 and bool(lib.djv_mlp_sparse_fused_single_batch(batch, d, rows))
+
     def can_fuse_after_exchange(self, partial, idx) -> bool:
         """Whether decode_after_exchange applies: a comm that producers push into, a sparse step, and a shape
         the one-pass kernel takes."""
-        if not (FUSED_MLP and self.push_comm is not None and idx is not None and self.activation == "relu"):
+        if self.push_comm is None or idx is None or partial.dim() != 3 or partial.size(1) != 1:
             return False
-        if partial.dim() != 3 or partial.size(1) != 1 or self.push_comm.pushed_seq(partial) is None:
+        if self.push_comm.pushed_seq(partial) is None:
             return False
-        return bool(_lib.load().djv_mlp_sparse_fused_supported(partial.size(0), partial.size(2), idx.numel()))
+        return self.fuses_after_exchange(partial.size(0), partial.size(2), idx.numel())
 
     def decode_after_exchange(self, partial, residual, norm, idx):
         """The block's second half in one kernel: residual = sum over ranks(partial) + residual;
@@ -549,7 +561,8 @@ class ParallelMHASparseAttMlp(nn.Module):
                 # the head predictor forks after the QKV projection: its GEMVs then overlap the attention kernel,
                 # which leaves HBM mostly idle, instead of taking the multiprocessors just before the projection
                 predict_heads()
-                if MLP_IDX_JOIN == "attend" and self.push_comm is not None:
+                if (MLP_IDX_JOIN == "attend" and mlp_idx is not None and self.mlp_ref is not None
+                        and self.mlp_ref.fuses_after_exchange(x.size(0), self.embed_dim, mlp_idx.numel())):
                     _wait_ready(mlp_idx)
 
             out = self._decode_attention(x, head_idx if self.sparse_attention else None, inference_params,

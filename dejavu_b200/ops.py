@@ -172,16 +172,18 @@ def dense_transposed_gemv(x: torch.Tensor, weight_t: torch.Tensor, bias: Optiona
     return output
 
 
-def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None, push_comm=None):
+def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None, push_comm=None, fused=False):
     """x (batch, d); W1 (4d, d); W2t (4d, d) = W2 transposed, contiguous; bias1 (4d); bias2 (d).
-    One kernel and one pass over the gathered rows when the shape allows it (batch <= 4, d % 64 == 0),
-    otherwise gather_gemv followed by gather_transposed_gemv."""
+    gather_gemv followed by gather_transposed_gemv, as in the reference; with fused=True one kernel and one pass
+    over the gathered rows (batch <= 4, d % 64 == 0; see mlp_sparse_fused_supported). Measured on a B200 the two
+    kernels are the faster form when the call stands alone; the one-pass kernel is for the decode step of a
+    tensor-parallel shard, where it also takes in the exchange in front of it (mlp_sparse_after_exchange)."""
     batch, N = x.shape
     (M,) = idx.shape
-    fused = (push_comm is None and x.is_cuda and x.dtype == torch.float16 and W1.dtype == torch.float16
-             and W2t.dtype == torch.float16 and W1.stride(1) == 1 and W2t.stride(1) == 1
-             and W1.shape[1] == N and W2t.shape[1] == N
-             and _lib.load().djv_mlp_sparse_fused_supported(batch, N, M))
+    if fused:
+        assert push_comm is None and mlp_sparse_fused_supported(batch, N, M)
+        assert x.dtype == W1.dtype == W2t.dtype == torch.float16 and W1.stride(1) == 1 and W2t.stride(1) == 1
+        assert W1.shape[1] == N and W2t.shape[1] == N
     if not fused:
         x = gather_gemv(x, W1, idx, bias1, activation="relu")
         return gather_transposed_gemv(x, W2t, idx, bias2, push_comm=push_comm)
@@ -201,6 +203,10 @@ def mlp_sparse(x, W1, W2t, idx, bias1=None, bias2=None, push_comm=None):
          _ptr(bias1), _ptr(bias2), batch, N, M, W1.shape[0], W1.stride(0), W2t.stride(0), idx64,
          scratch.data_ptr(), scratch.numel(), _stream())
     return output
+
+
+def mlp_sparse_fused_supported(batch: int, N: int, M: int) -> bool:
+    return bool(_lib.load().djv_mlp_sparse_fused_supported(batch, N, M))
 
 
 def mlp_sparse_after_exchange(comm, partial, residual, norm_weight, norm_bias, eps, W1, W2t, idx, bias1=None,

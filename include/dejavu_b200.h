@@ -148,6 +148,9 @@ int djv_mlp_sparse(void *y, void *h, const void *w1, const void *w2t, const void
  * this process (0 in a healthy run; synchronises).
  * ------------------------------------------------------------------------------------------- */
 int djv_mlp_sparse_fused_supported(int B, int N, int M);
+/* 1 when the index list is short enough for every block to keep all of its rows in flight at once (the regime
+ * the one-pass kernel is built for: a tensor-parallel shard's few hundred rows); host-side heuristic. */
+int djv_mlp_sparse_fused_single_batch(int B, int N, int M);
 size_t djv_mlp_sparse_fused_scratch_bytes(int B, int N, int M);
 unsigned djv_mlp_ring_timeouts(void);
 unsigned djv_mlp_ring_bad_indices(void);

@@ -67,15 +67,15 @@ def test_mlp_sparse_fused_vs_oracle(cuda, Z, N, M, B, kind):
     W1, W2t, b1, b2, x, idx = _mlp_inputs(gen, Z, N, M, B, kind)
     dev = [t.to(cuda) for t in (W1, W2t, b1, b2, x, idx)]
     before = lib.djv_launch_count()
-    got = ops.mlp_sparse(dev[4], dev[0], dev[1], dev[5], dev[2], dev[3])
+    got = ops.mlp_sparse(dev[4], dev[0], dev[1], dev[5], dev[2], dev[3], fused=True)
     assert lib.djv_launch_count() == before + 1, "the sparse MLP must be one launch"
     ref = O.mlp_sparse(x, W1, W2t, idx, b1, b2)
     tol = max(ATOL, 2e-3 * float(ref.float().abs().max()))
     close(got, ref, atol=tol)
-    again = ops.mlp_sparse(dev[4], dev[0], dev[1], dev[5], dev[2], dev[3])
+    again = ops.mlp_sparse(dev[4], dev[0], dev[1], dev[5], dev[2], dev[3], fused=True)
     assert torch.equal(got, again), "summation order must be fixed"
     # without biases
-    close(ops.mlp_sparse(dev[4], dev[0], dev[1], dev[5], None, None), O.mlp_sparse(x, W1, W2t, idx, None, None), atol=tol)
+    close(ops.mlp_sparse(dev[4], dev[0], dev[1], dev[5], None, None, fused=True), O.mlp_sparse(x, W1, W2t, idx, None, None), atol=tol)
     # and the two-kernel formulation of the same product
     h = ops.gather_gemv(dev[4], dev[0], dev[5], dev[2], "relu")
     two = ops.gather_transposed_gemv(h, dev[1], dev[5], dev[3])
@@ -90,11 +90,11 @@ def test_mlp_sparse_fused_with_early_weight_stream(cuda):
 
     gen = torch.Generator().manual_seed(3)
     W1, W2t, b1, b2, x, idx = [t.to(cuda) for t in _mlp_inputs(gen, 6144, 12288, 700, 1, "rand32")]
-    want = ops.mlp_sparse(x, W1, W2t, idx, b1, b2)
+    want = ops.mlp_sparse(x, W1, W2t, idx, b1, b2, fused=True)
     torch.cuda.synchronize()
     with ops.indices_ready(True):
         filler = x * 2  # some kernel in front
-        got = ops.mlp_sparse(x, W1, W2t, idx, b1, b2)
+        got = ops.mlp_sparse(x, W1, W2t, idx, b1, b2, fused=True)
     assert torch.equal(got, want) and filler is not None
 
 

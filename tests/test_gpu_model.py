@@ -26,7 +26,8 @@ def build(cfg, cuda, seed=0, local_exchange=False):
     if local_exchange:
         from dejavu_b200.comm import TensorParallelComm
 
-        model.transformer.enable_fused_allreduce(TensorParallelComm(None, cuda, max_bytes=cfg.hidden_size * 2))
+        model.transformer.enable_fused_allreduce(TensorParallelComm(None, cuda, max_bytes=cfg.hidden_size * 2),
+                                                 fused_mlp="1")
     return model
 
 

@@ -98,7 +98,7 @@ def _worker(rank, world, init_file, out_file):
         _log(rank, "nccl eager decode done")
         comm = TensorParallelComm(pg, dev, max_bytes=cfg.hidden_size * 2)
         _log(rank, "comm created")
-        model.transformer.enable_fused_allreduce(comm)
+        model.transformer.enable_fused_allreduce(comm, fused_mlp="1")
         fused_logits, fused_tokens, _ = _decode_run(model, cfg, ids, steps, dev, pg, rank, world, record=False)
         status = comm.status()
         _log(rank, f"fused eager decode done, status {status}")
