@@ -278,12 +278,13 @@ extern "C" int djv_gather_gemv(void *y, const void *w, const void *x, const void
     if (rc) return rc;
     return check_launch("gather_gemv");
   }
-  // Enough activation rows make this a real small-N contraction: tensor cores. Measured cross-over on B200
-  // (d = 12288): above 8 rows always; for 3..8 rows only when there are >= 256 tiles of 16 gathered rows
-  // (the CUDA-core kernel, one slice of <= 8 rows at a time, wins on short index lists).
-  static const int k_mma_min_b = env_int("DJV_MMA_MIN_B", 3);
+  // Enough activation rows make this a real small-N contraction: tensor cores, from 5 rows up (the kernel splits the
+  // reduction over the blocks of a cluster when the index list is short); for 3 and 4 rows only when there are
+  // >= 256 tiles of 16 gathered rows, below that the CUDA-core kernel wins.
+  static const int k_mma_min_b = env_int("DJV_MMA_MIN_B", 3);         // development knobs
+  static const int k_mma_always_b = env_int("DJV_MMA_ALWAYS_B", 5);
   static const int k_mma_min_tiles = env_int("DJV_MMA_MIN_TILES", 256);
-  if (B > 8 || (B >= k_mma_min_b && ceil_div(M, MM_ROWS) >= k_mma_min_tiles)) {
+  if (B >= k_mma_always_b || (B >= k_mma_min_b && ceil_div(M, MM_ROWS) >= k_mma_min_tiles)) {
     rc = rowdot_mma(B, act, static_cast<__half *>(y), static_cast<const __half *>(w),
                     static_cast<const __half *>(x), idx, static_cast<const __half *>(bias), M, N, ldw,
                     idx_is_64, st);

@@ -10,6 +10,8 @@
 // activations are permuted the same way along k, and a dot product does not care.
 // Traffic is unchanged: every gathered row is read once.
 #pragma once
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace djv {
@@ -25,6 +27,9 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Short index lists: M / 16 blocks would leave most of the device idle, so the reduction dimension is also split
+// over the blocks of a thread-block cluster (grid (tiles, S), cluster (1, S)): block s of a cluster takes k-blocks
+// s*8 + warp, then strides by 8*S; block 0 adds the others' sums through distributed shared memory, in block order.
 template <int NT, int ACT>  // NT groups of 8 activation rows
 __global__ void __launch_bounds__(MM_THREADS)
 rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
@@ -32,6 +37,8 @@ rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __
                   long long ldw, int idx64, int B) {
   pdl_prologue();
   __shared__ float red[MM_WARPS][NT][MM_ROWS][8];
+  __shared__ float bsum[NT][MM_ROWS][8];
+  const int S = gridDim.y, sblk = blockIdx.y;
   const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
   const int g = lane / 4, t = lane % 4;
   const int m0 = blockIdx.x * MM_ROWS;
@@ -50,11 +57,11 @@ rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __
   const int kblocks = (N + 31) / 32;
   // weight and activation loads of U k-blocks are all issued before the first MMA needs them
   constexpr int U = (NT <= 2) ? 4 : 2;
-  for (int kb0 = warp; kb0 < kblocks; kb0 += MM_WARPS * U) {
+  for (int kb0 = sblk * MM_WARPS + warp; kb0 < kblocks; kb0 += MM_WARPS * S * U) {
     uint4 a_lo[U], a_hi[U], xv[U][NT];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int k = (kb0 + u * MM_WARPS) * 32 + t * 8;
+      const int k = (kb0 + u * MM_WARPS * S) * 32 + t * 8;
       const bool ok = k < N;  // N % 8 == 0: a 16-byte piece is inside the row or entirely outside
       a_lo[u] = (ok && r_lo >= 0) ? ld_stream16(w_lo + k) : make_uint4(0, 0, 0, 0);
       a_hi[u] = (ok && r_hi >= 0) ? ld_stream16(w_hi + k) : make_uint4(0, 0, 0, 0);
@@ -83,25 +90,51 @@ rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __
     red[warp][j][g + 8][2 * t + 1] = acc[j][3];
   }
   __syncthreads();
-  for (int o = tid; o < NT * MM_ROWS * 8; o += MM_THREADS) {
-    const int j = o / (MM_ROWS * 8), row = (o / 8) % MM_ROWS, c = o % 8;
-    const int m = m0 + row, tok = j * 8 + c;
-    if (m < M && tok < B) {
+  namespace cgx = cooperative_groups;
+  cgx::cluster_group cluster = cgx::this_cluster();
+  if (S > 1) {
+    // this block's sums, then the cluster's
+    for (int o = tid; o < NT * MM_ROWS * 8; o += MM_THREADS) {
+      const int j = o / (MM_ROWS * 8), row = (o / 8) % MM_ROWS, c = o % 8;
       float s = 0.f;
 #pragma unroll
       for (int w2 = 0; w2 < MM_WARPS; ++w2) s += red[w2][j][row][c];
-      if (bias != nullptr) s += __half2float(bias[load_index(idx, m, idx64)]);
-      Y[(size_t)tok * M + m] = __float2half_rn(apply_act<ACT>(s));
+      bsum[j][row][c] = s;
+    }
+    cluster.sync();
+  }
+  if (sblk == 0) {
+    for (int o = tid; o < NT * MM_ROWS * 8; o += MM_THREADS) {
+      const int j = o / (MM_ROWS * 8), row = (o / 8) % MM_ROWS, c = o % 8;
+      const int m = m0 + row, tok = j * 8 + c;
+      if (m < M && tok < B) {
+        float s = 0.f;
+        if (S > 1) {
+          for (int q = 0; q < S; ++q) s += cluster.map_shared_rank(&bsum[0][0][0], q)[o];
+        } else {
+#pragma unroll
+          for (int w2 = 0; w2 < MM_WARPS; ++w2) s += red[w2][j][row][c];
+        }
+        if (bias != nullptr) s += __half2float(bias[load_index(idx, m, idx64)]);
+        Y[(size_t)tok * M + m] = __float2half_rn(apply_act<ACT>(s));
+      }
     }
   }
+  if (S > 1) cluster.sync();  // no block leaves while block 0 may still read its sums
 }
 
 template <int NT>
 inline int launch_rowdot_mma(int act, __half *Y, const __half *W, const __half *X, const void *idx,
                              const __half *bias, int M, int N, long long ldw, int idx64, int B, cudaStream_t st) {
-  const int grid = ceil_div(M, MM_ROWS);
-#define DJV_MM(ACT_) \
-  djv::launch_kernel(rowdot_mma_kernel<NT, ACT_>, grid, MM_THREADS, 0, st, Y, W, X, idx, bias, M, N, ldw, idx64, B)
+  const int tiles = ceil_div(M, MM_ROWS);
+  // split the reduction over 2, 4 or 8 blocks while that still leaves less than two blocks per multiprocessor
+  // and every block at least 8 k-blocks of 32
+  int S = 1;
+  while (S < 8 && tiles * S * 2 <= 2 * sm_count() && (N + 31) / 32 >= MM_WARPS * S * 2 * 8) S *= 2;
+  const dim3 grid(tiles, S), cluster(1, S, 1);
+#define DJV_MM(ACT_)                                                                                              \
+  djv::launch_kernel_cluster(rowdot_mma_kernel<NT, ACT_>, grid, dim3(MM_THREADS), 0, st, cluster, Y, W, X, idx, bias, \
+                             M, N, ldw, idx64, B)
   switch (act) {
     case DJV_ACT_ID: DJV_MM(DJV_ACT_ID); break;
     case DJV_ACT_RELU: DJV_MM(DJV_ACT_RELU); break;

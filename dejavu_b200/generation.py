@@ -96,7 +96,7 @@ def update_graph_cache(model, cache, batch_size, seqlen_og, max_seqlen, tensor_p
     cache.position_ids = torch.full((batch_size, 1), seqlen_og, dtype=torch.long, device=device)
     # the decode state must describe a decodable position while warming up
     for layer in model.transformer.layers:
-        layer.mixer.reset_decode_state(seqlen_og, device, max_seqlen)
+        layer.mixer.reset_decode_state(seqlen_og, device, max_seqlen, batch_size)
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
     def step():

@@ -232,9 +232,15 @@ class ParallelSP(nn.Module):
         self.K = K // _world(process_group)
 
     def forward(self, x):
-        x = ops.dense_gemv(x.view(1, self.embed_dim), self.fc0.weight)  # 1 x low_rank
+        """x (1, 1, d) -> logits (out,). A batch (B, 1, d) gives ONE score vector: the sum of the sequences' logits
+        (fp32 sum of the fp16 logits, rounded to fp16), so that the whole batch shares one index set per step, as
+        the reference's kernels expect (one idx for all rows, Dejavu/src/ops/triton/gather_gemv.py:198-254); its
+        decode path itself keeps a single sequence (mha_dejavu.py:1318, 1469)."""
+        x = ops.dense_gemv(x.reshape(-1, self.embed_dim), self.fc0.weight)  # B x low_rank
         x = ops.dense_gemv(x, self.fc1.weight)
-        return x.view(-1)
+        if x.size(0) == 1:
+            return x.view(-1)
+        return x.float().sum(0).to(x.dtype)
 
 
 class ParallelFusedMLPDejavu(nn.Module):
@@ -423,27 +429,31 @@ class ParallelMHASparseAttMlp(nn.Module):
         self._bufs = None
 
     # ---- device-resident decode state --------------------------------------------------------
-    def _decode_buffers(self, device, S):
+    def _decode_buffers(self, device, S, batch=1):
+        """Per-sequence state of the decode step (one lazy-K/V window, query and context buffer per sequence; the
+        sequences of a batch share the head selection, so their windows stay identical)."""
         n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
-        if self._bufs is None or self._bufs["S"] != S or self._bufs["state"].device != device:
+        if (self._bufs is None or self._bufs["S"] != S or self._bufs["device"] != device
+                or len(self._bufs["seqs"]) < batch):
             need = _lib.load().djv_attn_step_scratch_bytes(n, hd, S)
-            self._bufs = {
-                "S": S,
+            self._bufs = {"S": S, "device": device, "seqs": [{
                 "state": torch.zeros(_lib.ATTN_STATE_HDR + 3 * n, dtype=torch.int32, device=device),
                 "x_ring": torch.zeros(KV_WINDOW, d, dtype=torch.float16, device=device),
                 "q": torch.zeros(n, hd, dtype=torch.float16, device=device),
                 "ctx": torch.zeros(1, n, hd, dtype=torch.float16, device=device),
                 "scratch": torch.zeros(max(need, 4096), dtype=torch.uint8, device=device),
-            }
-        return self._bufs
+            } for _ in range(batch)]}
+        return self._bufs["seqs"]
 
-    def reset_decode_state(self, prompt_len: int, device, S: int):
-        b = self._decode_buffers(device, S)
-        call("djv_attn_state_reset", b["state"].data_ptr(), self.num_head_per_node, int(prompt_len), ops._stream())
+    def reset_decode_state(self, prompt_len: int, device, S: int, batch: int = 1):
+        for b in self._decode_buffers(device, S, batch):
+            call("djv_attn_state_reset", b["state"].data_ptr(), self.num_head_per_node, int(prompt_len), ops._stream())
 
     def decode_status(self) -> int:
         """0, or the negative status a kernel left in the state (synchronises)."""
-        return 0 if self._bufs is None else int(self._bufs["state"][3].item())
+        if self._bufs is None:
+            return 0
+        return min(int(b["state"][3].item()) for b in self._bufs["seqs"])
 
     # ---- prompt phase: dense ------------------------------------------------------------------
     def _prompt_attention(self, x, inference_params):
@@ -452,7 +462,6 @@ class ParallelMHASparseAttMlp(nn.Module):
         qkv = self.Wqkv(x).view(B, L, 3, n, hd)
         q, k, v = qkv.unbind(2)
         if inference_params is not None:
-            assert B == 1, "the sparse decode path keeps one sequence (mha_dejavu.py:1318, 1469)"
             k_cache, v_cache = inference_params.key_value_memory_dict[self.layer_idx]
             S = v_cache.shape[2]
             off = inference_params.sequence_len_offset
@@ -460,7 +469,7 @@ class ParallelMHASparseAttMlp(nn.Module):
             # K cache (B, n, hd/8, S, 8), V cache (B, n, S, hd)   (mha_dejavu.py:385-447)
             k_cache[:, :, :, :L, :] = k.permute(0, 2, 3, 1).reshape(B, n, hd // 8, 8, L).permute(0, 1, 2, 4, 3)
             v_cache[:, :, :L, :] = v.permute(0, 2, 1, 3)
-            self.reset_decode_state(L, x.device, S)
+            self.reset_decode_state(L, x.device, S, B)
         ctx = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                              is_causal=True, scale=self.softmax_scale)
         return ctx.transpose(1, 2).reshape(B, L, n * hd)
@@ -468,14 +477,17 @@ class ParallelMHASparseAttMlp(nn.Module):
     # ---- decode step ---------------------------------------------------------------------------
     def _decode_attention(self, x, head_idx, inference_params, between=None):
         """One decode step of this layer's attention; `between()` is called after the projection kernels are
-        queued and before the attention kernel (the place to fork look-ahead work onto a side stream)."""
+        queued and before the attention kernel (the place to fork look-ahead work onto a side stream).
+        A batch runs sequence by sequence through the same kernels (each sequence has its own window and caches;
+        the head selection is shared), after the first sequence the selected heads' weights come from L2."""
         n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
-        assert x.size(0) == 1, "the sparse decode path keeps one sequence (mha_dejavu.py:1318, 1469)"
+        B = x.size(0)
         k_cache, v_cache = inference_params.key_value_memory_dict[self.layer_idx]
+        assert k_cache.size(0) >= B and v_cache.size(0) >= B
         S = v_cache.shape[2]
-        b = self._decode_buffers(x.device, S)
+        seqs = self._decode_buffers(x.device, S, B)
         st = ops._stream()
-        xf = x.reshape(d).contiguous()
+        xf = x.reshape(B, d).contiguous()
         nnz = 0
         if head_idx is not None:
             assert head_idx.dtype == torch.int32
@@ -487,32 +499,36 @@ class ParallelMHASparseAttMlp(nn.Module):
         # an opened step means the state was written on a side stream whose event the main stream has waited on
         early = EARLY_PREFETCH and step_is_open == 1 and getattr(head_idx, "_ready_event", None) is not None
         with ops.indices_ready(early):
-            call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
-                 None if bias is None else bias.data_ptr(), xf.data_ptr(), b["x_ring"].data_ptr(), k_cache.data_ptr(),
-                 v_cache.data_ptr(), b["state"].data_ptr(), None if head_idx is None else head_idx.data_ptr(), nnz, d,
-                 n, hd, S, step_is_open, st)
+            for i, b in enumerate(seqs[:B]):
+                call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
+                     None if bias is None else bias.data_ptr(), xf[i].data_ptr(), b["x_ring"].data_ptr(),
+                     k_cache[i].data_ptr(), v_cache[i].data_ptr(), b["state"].data_ptr(),
+                     None if head_idx is None else head_idx.data_ptr(), nnz, d, n, hd, S, step_is_open, st)
         if between is not None:
             between()
-        call("djv_attn_step_attend", b["ctx"].data_ptr(), b["q"].data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
-             b["state"].data_ptr(), n, hd, S, float(self.softmax_scale), b["scratch"].data_ptr(),
-             b["scratch"].numel(), st)
-        out = torch.empty(1, d, dtype=x.dtype, device=x.device)
+        for i, b in enumerate(seqs[:B]):
+            call("djv_attn_step_attend", b["ctx"].data_ptr(), b["q"].data_ptr(), k_cache[i].data_ptr(),
+                 v_cache[i].data_ptr(), b["state"].data_ptr(), n, hd, S, float(self.softmax_scale),
+                 b["scratch"].data_ptr(), b["scratch"].numel(), st)
+        out = torch.empty(B, d, dtype=x.dtype, device=x.device)
         ob = self.out_proj.bias
-        state = b["state"]
-        eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
-        n_eff_ptr = state.data_ptr() + 4 * 2
         with ops.indices_ready(early):
-            if self.push_comm is not None:
-                seq = self.push_comm.next_seq()
-                call("djv_out_proj_sparse_push", self.push_comm.handle, seq, self.out_proj.weight.data_ptr(),
-                     b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n,
-                     hd, n, st)
-                self.push_comm.note_pushed(out, seq)
-            else:
-                call("djv_out_proj_sparse", out.data_ptr(), self.out_proj.weight.data_ptr(), b["ctx"].data_ptr(),
-                     eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n, hd, n, st)
+            for i, b in enumerate(seqs[:B]):
+                state = b["state"]
+                eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
+                n_eff_ptr = state.data_ptr() + 4 * 2
+                if self.push_comm is not None and B == 1:
+                    seq = self.push_comm.next_seq()
+                    call("djv_out_proj_sparse_push", self.push_comm.handle, seq, self.out_proj.weight.data_ptr(),
+                         b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d,
+                         n, hd, n, st)
+                    self.push_comm.note_pushed(out, seq)
+                else:
+                    call("djv_out_proj_sparse", out[i].data_ptr(), self.out_proj.weight.data_ptr(),
+                         b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n,
+                         hd, n, st)
         # the window advance is folded into the next step's first kernel (no djv_attn_step_finish launch)
-        return out.view(1, 1, d)
+        return out.view(B, 1, d)
 
     def forward(self, x, residual, head_idx=None, mlp_sp_logit=None, seqlen=None, inference_params=None, **kwargs):
         do_token_generation = x.size(1) == 1
@@ -535,18 +551,19 @@ class ParallelMHASparseAttMlp(nn.Module):
                 nxt = self.next_mixer if (decoding and FUSE_STEP_OPEN) else None
                 with _side(x, "att", after=residual) as done:
                     scores = self.sp(residual)
-                    if nxt is not None and nxt.sparse_attention and scores.dim() == 1:
+                    if nxt is not None and nxt.sparse_attention and scores.dim() == 1 and x.size(0) == 1:
                         # the selection is for the next layer's attention: open its decode step in the same
                         # kernel, so that layer starts with its QKV projection
                         S_next = inference_params.key_value_memory_dict[nxt.layer_idx][1].shape[2]
-                        state = nxt._decode_buffers(x.device, S_next)["state"]
+                        state = nxt._decode_buffers(x.device, S_next)[0]["state"]
                         idx = ops.topk_indices_open_step(scores, self.att_k, state, S_next)
                         idx._step_opened_for = nxt
                     else:
                         idx = ops.topk_indices(scores, self.att_k, torch.int32)
                     result["att_idx"] = idx
                     done(idx)
-                    if nxt is not None and nxt.sparse_attention and self.l2_prefetch_enabled():
+                    if (nxt is not None and nxt.sparse_attention and x.size(0) == 1
+                            and self.l2_prefetch_enabled()):
                         # the next layer's q, k, v slabs and out_proj columns of the heads just selected
                         n_n, hd_n = nxt.num_head_per_node, nxt.head_dim
                         wq = nxt.Wqkv.weight.view(3, n_n * hd_n, nxt.embed_dim)

@@ -82,55 +82,80 @@ class OracleDecoder:
 
     # -- prompt (dense) ----------------------------------------------------------------------------
     def prompt(self, ids: torch.Tensor) -> torch.Tensor:
-        """ids (P,) -> logits of the last position (vocab,)."""
-        P = ids.numel()
+        """ids (P,) -> logits of the last position (vocab,); ids (B, P) -> (B, vocab), one K/V history per
+        sequence."""
+        single = ids.dim() == 1
+        batch = ids[None] if single else ids
+        B, P = batch.shape
         sd = self.sd
-        h = (sd["transformer.embeddings.word_embeddings.weight"][ids].float()
-             + sd["transformer.embeddings.position_embeddings.weight"][:P].float()).to(self.dtype)
-        residual = None
+        ks = [[None] * B for _ in range(self.L)]
+        vs = [[None] * B for _ in range(self.L)]
+        out = []
+        for b in range(B):
+            row = batch[b]
+            h = (sd["transformer.embeddings.word_embeddings.weight"][row].float()
+                 + sd["transformer.embeddings.position_embeddings.weight"][:P].float()).to(self.dtype)
+            residual = None
+            for i in range(self.L):
+                x, residual = O.add_layernorm(h, residual, self._p(i, "norm1.weight"), self._p(i, "norm1.bias"),
+                                              self.cfg.layer_norm_epsilon)
+                qkv = self._lin(x, self._p(i, "mixer.Wqkv.weight"), self._p(i, "mixer.Wqkv.bias")).view(P, 3, self.H, self.hd)
+                q, k, v = qkv[:, 0].transpose(0, 1), qkv[:, 1].transpose(0, 1), qkv[:, 2].transpose(0, 1)
+                ks[i][b], vs[i][b] = k.contiguous(), v.contiguous()
+                s = torch.einsum("hqd,hkd->hqk", q.float() * self.hd ** -0.5, k.float())
+                s = s + torch.full((P, P), float("-inf")).triu(1)
+                ctx = torch.einsum("hqk,hkd->hqd", torch.softmax(s, -1), v.float()).to(self.dtype)
+                ctx = ctx.transpose(0, 1).reshape(P, self.d)
+                h = self._lin(ctx, self._p(i, "mixer.out_proj.weight"), self._p(i, "mixer.out_proj.bias"))
+                x, residual = O.add_layernorm(h, residual, self._p(i, "norm2.weight"), self._p(i, "norm2.bias"),
+                                              self.cfg.layer_norm_epsilon)
+                a = torch.relu(self._lin(x, self._p(i, "mlp.fc1.weight"), self._p(i, "mlp.fc1.bias")))
+                h = self._lin(a, self._p(i, "mlp.fc2.weight"), self._p(i, "mlp.fc2.bias"))
+            x, _ = O.add_layernorm(h, residual, sd["transformer.ln_f.weight"], sd["transformer.ln_f.bias"],
+                                   self.cfg.layer_norm_epsilon)
+            out.append(self._lin(x[-1:], sd["lm_head.weight"])[0])
         for i in range(self.L):
-            x, residual = O.add_layernorm(h, residual, self._p(i, "norm1.weight"), self._p(i, "norm1.bias"),
-                                          self.cfg.layer_norm_epsilon)
-            qkv = self._lin(x, self._p(i, "mixer.Wqkv.weight"), self._p(i, "mixer.Wqkv.bias")).view(P, 3, self.H, self.hd)
-            q, k, v = qkv[:, 0].transpose(0, 1), qkv[:, 1].transpose(0, 1), qkv[:, 2].transpose(0, 1)
-            self.k[i], self.v[i] = k.contiguous(), v.contiguous()
-            s = torch.einsum("hqd,hkd->hqk", q.float() * self.hd ** -0.5, k.float())
-            s = s + torch.full((P, P), float("-inf")).triu(1)
-            ctx = torch.einsum("hqk,hkd->hqd", torch.softmax(s, -1), v.float()).to(self.dtype)
-            ctx = ctx.transpose(0, 1).reshape(P, self.d)
-            h = self._lin(ctx, self._p(i, "mixer.out_proj.weight"), self._p(i, "mixer.out_proj.bias"))
-            x, residual = O.add_layernorm(h, residual, self._p(i, "norm2.weight"), self._p(i, "norm2.bias"),
-                                          self.cfg.layer_norm_epsilon)
-            a = torch.relu(self._lin(x, self._p(i, "mlp.fc1.weight"), self._p(i, "mlp.fc1.bias")))
-            h = self._lin(a, self._p(i, "mlp.fc2.weight"), self._p(i, "mlp.fc2.bias"))
-        x, _ = O.add_layernorm(h, residual, sd["transformer.ln_f.weight"], sd["transformer.ln_f.bias"],
-                               self.cfg.layer_norm_epsilon)
+            self.k[i], self.v[i] = torch.stack(ks[i]), torch.stack(vs[i])  # (B, H, S, hd)
         self.step = 0
-        return self._lin(x[-1:], sd["lm_head.weight"])[0]
+        return out[0] if single else torch.stack(out)
 
     # -- one decode step ---------------------------------------------------------------------------
-    def decode(self, token: int, pos: int, forced: Optional[List[dict]] = None):
-        """Returns (logits (vocab,), chosen) where chosen[i] = {"mlp_idx": ..., "att_idx": ...} are the sets
-        layer i produced (mlp_idx: used by layer i's own MLP; att_idx: for layer i+1's attention).
-        forced[i] holds the sets another implementation produced at layer i (or None entries)."""
+    def decode(self, token, pos: int, forced: Optional[List[dict]] = None):
+        """token: int -> (logits (vocab,), chosen); a list of B ints (one per sequence, all at position `pos`) ->
+        (logits (B, vocab), chosen). chosen[i] = {"mlp_idx": ..., "att_idx": ...} are the sets layer i produced
+        (mlp_idx: used by layer i's own MLP; att_idx: for layer i+1's attention); forced[i] holds the sets another
+        implementation produced at layer i (or None entries).
+        Batches share ONE index set per layer and step: the top-K of the predictor logits summed over the batch
+        (fp32 sum of the fp16 logits, rounded to fp16). The reference's decode path keeps a single sequence
+        (Dejavu/src/models/modules/mha_dejavu.py:1318, 1469); its kernels take one index list for all rows of a
+        batch (Dejavu/src/ops/triton/gather_gemv.py:198-254), which is what this rule feeds."""
+        single = not isinstance(token, (list, tuple))
+        tokens = torch.tensor([token] if single else list(token))
+        B = tokens.numel()
         sd, eps = self.sd, self.cfg.layer_norm_epsilon
-        h = (sd["transformer.embeddings.word_embeddings.weight"][token].float()
-             + sd["transformer.embeddings.position_embeddings.weight"][pos].float()).to(self.dtype)[None]
+        h = (sd["transformer.embeddings.word_embeddings.weight"][tokens].float()
+             + sd["transformer.embeddings.position_embeddings.weight"][pos].float()).to(self.dtype)
         residual, mlp_logit, att_idx = None, None, None
         flush = (self.step % O.KV_WINDOW) == O.KV_WINDOW - 1
         chosen = []
+
+        def shared(scores):  # (B, n) per-sequence logits -> the batch's scores
+            return scores[0] if B == 1 else scores.float().sum(0).to(self.dtype)
+
         for i in range(self.L):
             fi = forced[i] if forced is not None else {}
             x, residual = O.add_layernorm(h, residual, self._p(i, "norm1.weight"), self._p(i, "norm1.bias"), eps)
             # attention over heads att_idx (all heads for layer 0, dense models and flush steps)
-            qkv = self._lin(x, self._p(i, "mixer.Wqkv.weight"), self._p(i, "mixer.Wqkv.bias")).view(3, self.H, self.hd)
-            self.k[i] = torch.cat([self.k[i], qkv[1][:, None]], 1)
-            self.v[i] = torch.cat([self.v[i], qkv[2][:, None]], 1)
+            qkv = self._lin(x, self._p(i, "mixer.Wqkv.weight"), self._p(i, "mixer.Wqkv.bias")).view(B, 3, self.H, self.hd)
+            if self.k[i].dim() == 3:  # histories written by older callers: (H, S, hd)
+                self.k[i], self.v[i] = self.k[i][None], self.v[i][None]
+            self.k[i] = torch.cat([self.k[i], qkv[:, 1][:, :, None]], 2)
+            self.v[i] = torch.cat([self.v[i], qkv[:, 2][:, :, None]], 2)
             heads = torch.arange(self.H) if (att_idx is None or flush) else att_idx.long()
-            s = torch.einsum("hd,hkd->hk", qkv[0].float() * self.hd ** -0.5, self.k[i].float())
-            ctx = torch.einsum("hk,hkd->hd", torch.softmax(s, -1), self.v[i].float()).to(self.dtype)
+            s = torch.einsum("bhd,bhkd->bhk", qkv[:, 0].float() * self.hd ** -0.5, self.k[i].float())
+            ctx = torch.einsum("bhk,bhkd->bhd", torch.softmax(s, -1), self.v[i].float()).to(self.dtype)
             Wo = self._p(i, "mixer.out_proj.weight").view(self.d, self.H, self.hd)
-            attn_out = O.out_proj_sparse(ctx[None], Wo, heads.int(), self._p(i, "mixer.out_proj.bias"))
+            attn_out = O.out_proj_sparse(ctx, Wo, heads.int(), self._p(i, "mixer.out_proj.bias"))
             # this layer's MLP neurons come from the previous layer's logits
             mlp_idx = None
             if mlp_logit is not None:
@@ -138,7 +163,8 @@ class OracleDecoder:
             # next layer's heads come from this layer's attention-input residual
             next_att_idx = None
             if self._att_k(i) is not None:
-                a_scores = O.predictor_scores(residual, self._p(i, "mixer.sp.fc0.weight"), self._p(i, "mixer.sp.fc1.weight"))[0]
+                a_scores = shared(O.predictor_scores(residual, self._p(i, "mixer.sp.fc0.weight"),
+                                                     self._p(i, "mixer.sp.fc1.weight")))
                 next_att_idx = self._select(a_scores, self._att_k(i), fi.get("att_idx"), f"layer {i} att_idx")
             x, residual = O.add_layernorm(attn_out, residual, self._p(i, "norm2.weight"), self._p(i, "norm2.bias"), eps)
             W1, b1 = self._p(i, "mlp.fc1.weight"), self._p(i, "mlp.fc1.bias")
@@ -149,9 +175,11 @@ class OracleDecoder:
                 h = self._lin(torch.relu(self._lin(x, W1, b1)), W2, b2)
             mlp_logit = None
             if self._mlp_k() is not None:
-                mlp_logit = O.predictor_scores(residual, self._p(i, "mlp.sp.fc0.weight"), self._p(i, "mlp.sp.fc1.weight"))[0]
+                mlp_logit = shared(O.predictor_scores(residual, self._p(i, "mlp.sp.fc0.weight"),
+                                                      self._p(i, "mlp.sp.fc1.weight")))
             att_idx = next_att_idx
             chosen.append({"mlp_idx": mlp_idx, "att_idx": next_att_idx})
         x, _ = O.add_layernorm(h, residual, sd["transformer.ln_f.weight"], sd["transformer.ln_f.bias"], eps)
         self.step += 1
-        return self._lin(x, sd["lm_head.weight"])[0], chosen
+        logits = self._lin(x, sd["lm_head.weight"])
+        return (logits[0] if single else logits), chosen

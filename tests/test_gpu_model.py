@@ -99,6 +99,53 @@ def test_decode_matches_oracle(cuda, mlp_K, att_K, local_exchange):
             m.transformer.comm.close()
 
 
+@pytest.mark.parametrize("B,mlp_K,att_K,local_exchange", [(3, 256, 2, False), (4, 256, 2, True), (2, 1024, 4, False),
+                                                         (5, 256, 2, True)])
+def test_batched_decode_shares_one_index_set_and_matches_oracle(cuda, B, mlp_K, att_K, local_exchange):
+    """Several sequences decode in lockstep with ONE index set per layer and step (top-K of the predictor logits
+    summed over the batch); every sequence's logits follow the oracle, which applies the same rule."""
+    from dejavu_b200.generation import InferenceParams, allocate_kv_cache
+
+    cfg = tiny_config(mlp_K, att_K, n_layer=3)
+    model = build(cfg, cuda, local_exchange=False)
+    if local_exchange:
+        from dejavu_b200.comm import TensorParallelComm
+
+        model.transformer.enable_fused_allreduce(TensorParallelComm(None, cuda, max_bytes=B * cfg.hidden_size * 2),
+                                                 fused_mlp="1")
+    oracle = OracleDecoder(model.state_dict(), cfg, score_margin=1e-2)
+    gen = torch.Generator().manual_seed(B)
+    P, steps = 6, 20  # crosses a 16-step lazy-K/V window
+    ids = torch.randint(0, cfg.vocab_size, (B, P), generator=gen)
+    rec, handles = record_selections(model)
+    ip = InferenceParams(max_sequence_len=P + steps, max_batch_size=B,
+                         key_value_memory_dict=allocate_kv_cache(model, B, P + steps, cuda))
+    rec.append({})
+    with torch.inference_mode():
+        logits = model(ids.to(cuda), inference_params=ip).logits[:, -1].float().cpu()
+    ref = oracle.prompt(ids)
+    assert torch.allclose(logits, ref.float(), atol=3e-2, rtol=3e-2)
+    ip.sequence_len_offset = P
+    for t in range(steps):
+        toks = logits.argmax(-1)
+        rec.append({})
+        with torch.inference_mode():
+            logits = model(toks.view(B, 1).to(cuda), position_ids=torch.full((B, 1), P + t, device=cuda),
+                           inference_params=ip).logits[:, -1].float().cpu()
+        ip.sequence_len_offset += 1
+        forced = [rec[-1].get(i, {}) for i in range(cfg.n_layer)]
+        ref, _ = oracle.decode(toks.tolist(), P + t, forced=forced)
+        assert torch.allclose(logits, ref.float(), atol=3e-2, rtol=3e-2), \
+            f"step {t}: max diff {(logits - ref.float()).abs().max().item()}"
+    for m in model.transformer.layers:
+        assert m.mixer.decode_status() == 0
+    for h in handles:
+        h.remove()
+    if model.transformer.comm is not None:
+        assert model.transformer.comm.status() == 0
+        model.transformer.comm.close()
+
+
 @pytest.mark.parametrize("local_exchange", [False, True])
 def test_cuda_graph_decode_equals_eager(cuda, local_exchange):
     cfg = tiny_config(256, 2)
