@@ -44,9 +44,11 @@ FUSE_STEP_OPEN = os.environ.get("DJV_FUSE_STEP_OPEN", "1") != "0"
 PUSH_PARTIALS = os.environ.get("DJV_PUSH_PARTIALS", "1") != "0"
 # kernels whose index list is known to be complete prefetch weights before their PDL wait (development knob)
 EARLY_PREFETCH = os.environ.get("DJV_EARLY_PREFETCH", "1") != "0"
-# with a comm: exchange + residual + LayerNorm + fc1 + ReLU + fc2 (+ send) of a block in one kernel. "auto": for a
-# real tensor-parallel group when the shard's index list is short enough to be in flight at once; "1" / "0" force
-FUSED_MLP = os.environ.get("DJV_FUSED_MLP", "auto")
+# with a comm: exchange + residual + LayerNorm + fc1 + ReLU + fc2 (+ send) of a block in one kernel. "0" (default):
+# off, the separate kernels measured faster at every tensor-parallel degree (OPT-175B TP8: 5.18 against 6.25
+# ms/token, OPT-66B TP8: 3.06 against 3.15); "1": on wherever the shape allows; "auto": on for a real
+# tensor-parallel group when the shard's index list is short enough to be in flight at once
+FUSED_MLP = os.environ.get("DJV_FUSED_MLP", "0")
 # where the main stream joins the side stream that selects this layer's MLP rows: "attend" = before the attention
 # kernel (the fused MLP kernel then follows out_proj with a single programmatic edge and streams its weights while
 # out_proj runs), "mlp" = right before the MLP (development knob)
