@@ -457,7 +457,8 @@ def main():
     t_build = time.time() - t_build
 
     K, W, P = args.steps, args.warmup, args.promptlen
-    S = P + 2 * (W + K) + 64
+    PRE = 96  # untimed replays under the clock sampler before the timed region
+    S = P + 2 * (W + K) + 64 + PRE
     gen = torch.Generator().manual_seed(0)
     prompt_all = torch.randint(0, cfg.vocab_size, (max([args.batch] + [int(t.split(":")[2]) for t in
                                (args.sweep or "").split(",") if t.count(":") == 2]), P), generator=gen).to(dev)
@@ -480,12 +481,10 @@ def main():
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             with ClockSampler(local_rank) as clocks:
-                # the sampler needs a moment to come up (several ranks start one each): keep the GPU under the same
-                # load with untimed replays until it has delivered a sample, then time
-                t_wait = time.time()
-                while not clocks.lines and time.time() - t_wait < 3.0:
+                # the sampler needs a moment to come up: keep the GPU under the same load with a FIXED number of
+                # untimed replays first (the same on every rank: a replay is a collective step), then time
+                for _ in range(PRE):
                     cache.graph.replay()
-                    torch.cuda.synchronize()
                 barrier()
                 torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see the timed region only
                 e0.record()
@@ -494,12 +493,6 @@ def main():
                 e1.record()
                 barrier()
                 torch.cuda.profiler.stop()
-                if len(clocks.lines) < 2:  # a very short timed region: one more sample under the same load
-                    t_wait = time.time()
-                    n0 = len(clocks.lines)
-                    while len(clocks.lines) == n0 and time.time() - t_wait < 1.0:
-                        cache.graph.replay()
-                        torch.cuda.synchronize()
             ms = max_over_ranks(e0.elapsed_time(e1) / K)
             # end to end: host token in, host token out, every step
             tok_h = torch.zeros(Bt, 1, dtype=torch.long).pin_memory()
@@ -507,7 +500,7 @@ def main():
             out_h = torch.zeros(Bt, 1, dtype=torch.long).pin_memory()
             out_h.copy_(cache.next_token)
             torch.cuda.synchronize()
-            position = P + W + K
+            position = P + W + PRE + K
             barrier()
             t0 = time.perf_counter()
             for _ in range(K):

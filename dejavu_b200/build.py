@@ -50,14 +50,17 @@ def _stale(target: Path, deps: list[Path]) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """DJV_NVCC_FLAGS in the environment adds flags (e.g. -DDJV_RING_TRACE for the phase stamps of the one-pass
+    MLP kernel; use --force, the flag is not part of the staleness check)."""
     nvcc = _nvcc()
+    extra = os.environ.get("DJV_NVCC_FLAGS", "").split()
     OBJ.mkdir(exist_ok=True)
     headers = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "dejavu_b200.h"]
     jobs = []
     for src in sources():
         obj = OBJ / (src.stem + ".o")
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")

@@ -26,8 +26,13 @@ from . import oracle as O
 
 
 class OracleDecoder:
-    def __init__(self, state_dict: Dict[str, torch.Tensor], cfg, num_shards: int = 1, score_margin: float = 2e-3):
+    def __init__(self, state_dict: Dict[str, torch.Tensor], cfg, num_shards: int = 1, score_margin: float = 2e-3,
+                 cache_fp32: bool = False):
+        """cache_fp32: keep an fp32 copy of every matrix after its first use (wide models: converting a
+        12288 x 49152 matrix at every call dominates the run time otherwise)."""
         self.sd = {k: v.detach().cpu() for k, v in state_dict.items()}
+        self._fp32 = {} if cache_fp32 else None
+        self.free_running_checks = 0  # selections that were decisive and therefore compared exactly
         self.cfg = cfg
         self.L, self.d, self.H = cfg.n_layer, cfg.hidden_size, cfg.n_head
         self.hd = self.d // self.H
@@ -43,7 +48,14 @@ class OracleDecoder:
         return self.sd[f"transformer.layers.{i}.{name}"]
 
     def _lin(self, x, w, b=None):
-        y = x.float() @ w.float().T
+        if self._fp32 is not None:
+            key = (w.data_ptr(), tuple(w.shape))
+            if key not in self._fp32:
+                self._fp32[key] = w.float()
+            wf = self._fp32[key]
+        else:
+            wf = w.float()
+        y = x.float() @ wf.T
         if b is not None:
             y = y + b.float()
         return y.to(self.dtype)
@@ -77,6 +89,15 @@ class OracleDecoder:
                 worst_in, best_out = sl.float()[f].min().item(), sl.float()[rest].max().item()
                 assert worst_in >= best_out - self.margin * max(1.0, abs(best_out)), \
                     f"{what}: not a top-{k_per_shard} set (min selected {worst_in} < max unselected {best_out})"
+                # free-running agreement: when this oracle's own K-th and (K+1)-th scores are further apart than
+                # the margin, there is only one admissible set, and the other implementation must have found it
+                own = O.topk_indices_fast(sl, k_per_shard)
+                mine = torch.ones(n, dtype=torch.bool)
+                mine[own] = False
+                gap = sl.float()[own].min().item() - sl.float()[mine].max().item()
+                if gap > self.margin * max(1.0, abs(best_out)):
+                    assert torch.equal(own.sort().values, f.sort().values), f"{what}: decisive scores, different set"
+                    self.free_running_checks += 1
             out.append(f.sort().values + r * n)
         return torch.cat(out)
 

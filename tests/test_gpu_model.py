@@ -99,6 +99,47 @@ def test_decode_matches_oracle(cuda, mlp_K, att_K, local_exchange):
             m.transformer.comm.close()
 
 
+@pytest.mark.parametrize("d,heads,mlp_K,att_K,steps", [(4096, 32, 2048, 12, 20), (9216, 72, 4096, 24, 10),
+                                                       (12288, 96, 4096, 32, 10)])
+def test_decode_matches_oracle_at_real_widths(cuda, d, heads, mlp_K, att_K, steps):
+    """Two layers at the hidden size, head count and sparsity of OPT-6.7B / 66B / 175B (BASELINE configs 2-4; ffn =
+    4 d, 128-wide heads; a small vocabulary keeps the LM head out of the way). Logit tolerance 3e-2 absolute and
+    relative: the logits of these random models are O(1) and carry the fp16 rounding of two residual blocks whose
+    sums run over up to 49152 terms in a different order than the oracle's."""
+    from dejavu_b200.generation import InferenceParams, allocate_kv_cache
+    from dejavu_b200.gpt import GPTLMHeadModel, apply_sparsity_knobs, opt_config
+
+    cfg = opt_config("opt-125m", n_layer=2, n_embd=d, hidden_size=d, n_head=heads, n_inner=4 * d, vocab_size=1024,
+                     max_position_embeddings=64, n_positions=64)
+    apply_sparsity_knobs(cfg, mlp_K, att_K, att_K)
+    model = GPTLMHeadModel(cfg, device=cuda, dtype=torch.float16).eval().init_random(3)
+    oracle = OracleDecoder(model.state_dict(), cfg, score_margin=2e-3, cache_fp32=True)
+    P = 8
+    ids = torch.randint(0, cfg.vocab_size, (1, P), generator=torch.Generator().manual_seed(d))
+    rec, handles = record_selections(model)
+    ip = InferenceParams(max_sequence_len=P + steps, max_batch_size=1,
+                         key_value_memory_dict=allocate_kv_cache(model, 1, P + steps, cuda))
+    rec.append({})
+    with torch.inference_mode():
+        logits = model(ids.to(cuda), inference_params=ip).logits[0, -1].float().cpu()
+    assert torch.allclose(logits, oracle.prompt(ids[0]).float(), atol=3e-2, rtol=3e-2)
+    ip.sequence_len_offset = P
+    for t in range(steps):
+        tok = int(logits.argmax())
+        rec.append({})
+        with torch.inference_mode():
+            logits = model(torch.tensor([[tok]], device=cuda), position_ids=torch.tensor([[P + t]], device=cuda),
+                           inference_params=ip).logits[0, -1].float().cpu()
+        ip.sequence_len_offset += 1
+        ref, _ = oracle.decode(tok, P + t, forced=[rec[-1].get(i, {}) for i in range(cfg.n_layer)])
+        assert torch.allclose(logits, ref.float(), atol=3e-2, rtol=3e-2), \
+            f"step {t}: max diff {(logits - ref.float()).abs().max().item()}"
+    assert oracle.free_running_checks > 0, "no selection was decisive enough to be compared exactly"
+    for h in handles:
+        h.remove()
+    assert all(m.mixer.decode_status() == 0 for m in model.transformer.layers)
+
+
 @pytest.mark.parametrize("B,mlp_K,att_K,local_exchange", [(3, 256, 2, False), (4, 256, 2, True), (2, 1024, 4, False),
                                                          (5, 256, 2, True)])
 def test_batched_decode_shares_one_index_set_and_matches_oracle(cuda, B, mlp_K, att_K, local_exchange):
