@@ -12,6 +12,7 @@
 #include "common.cuh"
 #include "rowaxpy.cuh"
 #include "rowdot_mma.cuh"
+#include "rowaxpy_mma.cuh"
 
 namespace djv {
 
@@ -305,6 +306,7 @@ extern "C" int djv_gather_gemv(void *y, const void *w, const void *x, const void
 
 extern "C" size_t djv_gather_transposed_gemv_scratch_bytes(int B, int N, int M) {
   if (B < 1 || N < 8 || M < 0) return 0;
+  if (B > RA_MAX_B) return rowaxpy_mma_scratch_bytes(B, N, M > 0 ? M : 1);  // tensor-core kernel, one pass
   // a call is cut into slices of up to 4 rows of x, and the plan depends on the slice's row count
   const int bs = B < 4 ? B : 4;
   size_t need = 0;
@@ -339,6 +341,12 @@ extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x,
   if (M <= ring_gemv_rows() && ring_shape_ok(B, N, M) && scratch_bytes >= djv_mlp_sparse_fused_scratch_bytes(B, N, M)) {
     rc = ring_fc2(static_cast<__half *>(y), static_cast<const __half *>(w), static_cast<const __half *>(x), idx,
                   static_cast<const __half *>(bias), B, N, M, ldw, idx_is_64, scratch, st, PushTarget{});
+    if (rc) return rc;
+    return check_launch("gather_transposed_gemv");
+  }
+  if (B > RA_MAX_B) {  // 5..32 activation rows: tensor cores, every gathered row read once
+    rc = rowaxpy_mma(B, static_cast<__half *>(y), static_cast<const __half *>(w), static_cast<const __half *>(x), idx,
+                     static_cast<const __half *>(bias), scratch, M, N, ldw, idx_is_64, st);
     if (rc) return rc;
     return check_launch("gather_transposed_gemv");
   }
