@@ -5,14 +5,16 @@
 // With this many activation rows the CUDA-core kernel would either keep 8*B sums per lane or re-read every
 // gathered row once per slice of 4 activation rows. Here the product is tiled as mma.sync m16n8k16 (fp16 in, fp32
 // accumulate): M = activation rows (16 per tile, 1 or 2 tiles), K = 16 gathered rows, N = 8 columns.
-// A warp owns 128 columns (two groups of 64) and walks the block's rows 16 at a time. Lane (g, t) (g = lane / 4,
-// t = lane % 4) loads 16 contiguous bytes (8 columns, g-th chunk of the 64-column group) of rows 2t, 2t+1, 2t+8,
-// 2t+9 of the 16: exactly the k positions its B fragments need, so the fragments are built in registers with
-// byte permutes (pairing the same column of two rows) and nothing goes through shared memory. The e-th of the 8
-// columns a lane holds feeds MMA number e of the group, whose "n" index is the chunk number g: MMA e of group j
-// produces columns j*64 + n*8 + e. The 8 lanes that share t read 128 contiguous bytes of a row; the two groups of
-// a warp make that 2 x 128 bytes per row and warp, 8 independent 16-byte loads in flight per lane.
-// The activations of a 16-row step (A fragments) come from x directly (4 bytes per register, L1-resident).
+// A warp owns 128 columns and walks the block's rows 16 at a time ("step"). The 16 x 256 bytes of a step go from
+// global to the warp's own shared-memory ring with 16-byte asynchronous copies (cp.async), D steps deep: 16
+// consecutive lanes copy the 256 contiguous bytes of one row, so every 8-lane group of a request covers one
+// full 128-byte line. (Loading straight into the B-fragment layout would have the 8 lanes of such a group touch
+// 4 different rows, 32 bytes each: four times the L1 requests per byte, measured at 0.2 of the HBM peak.)
+// ldmatrix.trans then hands each lane the (k, k+1) pairs of its fragment column. The rows of the ring are padded
+// to 272 bytes, which spreads the 8 row addresses of an ldmatrix over all banks.
+// The 16 activations per activation row that multiply a step (the A fragments) travel with it: 32 bytes per
+// activation row in the same ring stage, read back with ldmatrix. The row numbers of the block's rows (at most
+// 1024) are staged in shared memory once, before the first copy.
 // Rows are split over gridDim.y blocks; with more than one the per-block sums go to `partial` and a second small
 // kernel adds them in block order (deterministic), all columns in parallel.
 // Traffic: every gathered row is read once, whatever B is.
@@ -26,114 +28,180 @@ constexpr int RM_THREADS = 256;
 constexpr int RM_WARPS = RM_THREADS / WARP;
 constexpr int RM_WCOLS = 128;                   // columns per warp
 constexpr int RM_BCOLS = RM_WARPS * RM_WCOLS;   // columns per block
-constexpr int RM_GROUPS = RM_WCOLS / 64;        // 64-column groups per warp
+constexpr int RM_NT = RM_WCOLS / 8;             // 8-column MMA tiles per warp
+constexpr int RM_DEPTH1 = 5, RM_DEPTH2 = 4;     // steps in the ring of a warp, for 1 / 2 tiles of activation rows
+constexpr int RM_PITCH = RM_WCOLS * 2 + 16;     // bytes between the rows of a step in shared memory
+constexpr int RM_W_BYTES = 16 * RM_PITCH;       // the gathered rows of one step of one warp
+constexpr int RM_A_PITCH = 48;                  // bytes between the activation rows of a step (32 used)
+constexpr int RM_MAX_ROWS = 1024;               // rows per block (their row numbers are staged in shared memory)
+constexpr int RM_IDX_BYTES = RM_MAX_ROWS * 4;
+template <int NTM>
+struct RmStage {
+  static constexpr int BYTES = RM_W_BYTES + NTM * 16 * RM_A_PITCH;  // one step of one warp
+};
+template <int NTM, int D>
+struct RmSmem {
+  static constexpr size_t BYTES = RM_IDX_BYTES + (size_t)RM_WARPS * D * RmStage<NTM>::BYTES;
+};
 
-// same column of two rows -> one register: (lo, hi) halves of a and b
-__device__ __forceinline__ uint32_t pair_lo(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x5410); }
-__device__ __forceinline__ uint32_t pair_hi(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x7632); }
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst_smem, const void *src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// four 8x8 fp16 matrices: lane (g, t) gets elements [g][2t], [g][2t+1] of each ...
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr_smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr_smem)
+               : "memory");
+}
+// ... or, transposed on the way, elements [2t][g], [2t+1][g]
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr_smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr_smem)
+               : "memory");
+}
 
-template <int NTM>  // tiles of 16 activation rows
-__global__ void __launch_bounds__(RM_THREADS)
+template <int NTM, int D>  // tiles of 16 activation rows; steps in the ring
+__global__ void __launch_bounds__(RM_THREADS, 1)
 rowaxpy_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                    const void *__restrict__ idx, const __half *__restrict__ bias, float *__restrict__ partial,
                    int M, int N, long long ldw, int idx64, int B, int rows_per_block) {
+  extern __shared__ __align__(128) unsigned char rm_smem[];
+  constexpr int ST = RmStage<NTM>::BYTES;
   pdl_prologue();
   const int tid = threadIdx.x, warp = tid / WARP, lane = tid % WARP;
   const int g = lane / 4, t = lane % 4;
   const int col0 = blockIdx.x * RM_BCOLS + warp * RM_WCOLS;  // first column of this warp
   const int rs = blockIdx.y, RS = gridDim.y;
   const int m_begin = min(M, rs * rows_per_block), m_end = min(M, m_begin + rows_per_block);
+  const int nrows = m_end - m_begin, nsteps = (nrows + 15) / 16;
   const unsigned short *Xh = reinterpret_cast<const unsigned short *>(X);
+  int *idx_s = reinterpret_cast<int *>(rm_smem);  // row numbers of this block's rows
+  const uint32_t ring =
+      (uint32_t)__cvta_generic_to_shared(rm_smem) + RM_IDX_BYTES + (uint32_t)warp * (uint32_t)(D * ST);
 
-  float acc[NTM][RM_GROUPS][8][4];
+  for (int i = tid; i < nrows; i += RM_THREADS) idx_s[i] = (int)load_index(idx, m_begin + i, idx64);
+
+  float acc[NTM][RM_NT][4];
 #pragma unroll
   for (int mt = 0; mt < NTM; ++mt)
 #pragma unroll
-    for (int j = 0; j < RM_GROUPS; ++j)
+    for (int nt = 0; nt < RM_NT; ++nt)
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[mt][j][e][c] = 0.f;
+      for (int c = 0; c < 4; ++c) acc[mt][nt][c] = 0.f;
+  __syncthreads();
 
-  // the 4 rows of a 16-row step this lane loads: k = 2t, 2t+1, 2t+8, 2t+9
-  const int kq[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int m0 = m_begin; m0 < m_end; m0 += 16) {
-    uint4 wv[RM_GROUPS][4];
+  // copies: lanes 0-15 take the even rows of a step, lanes 16-31 the odd ones; a lane moves one 16-byte chunk
+  const int lrow = lane >> 4, lchunk = lane & 15;
+  const int lcol = col0 + lchunk * 8;  // N % 8 == 0: a chunk is inside the row or entirely outside
+  const bool col_ok = lcol < N;
+  // x[b, m .. m+7] can be copied 16 bytes at a time when those are aligned (m is a multiple of 8 here)
+  const bool a_async = (M % 8) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0;
+  // start the copies of step j: 16 gathered rows (zero-filled past the end of the block's rows) and, per
+  // activation row, the 16 values that multiply them (2 chunks of 8)
+  auto issue = [&](int j) {
+    const uint32_t dst = ring + (uint32_t)(j % D) * ST;
+    const int r0 = j * 16;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int m = m0 + kq[q];
-      const bool ok = m < m_end;
-      const long long r = ok ? load_index(idx, m, idx64) : 0;
-      const __half *wrow = W + r * ldw;
+    for (int i = 0; i < 8; ++i) {
+      const int k = 2 * i + lrow;
+      const bool ok = r0 + k < nrows && col_ok;
+      const __half *src = ok ? W + (long long)idx_s[r0 + k] * ldw + lcol : W;
+      cp_async16_zfill(dst + (uint32_t)k * RM_PITCH + (uint32_t)lchunk * 16, src, ok ? 16 : 0);
+    }
+    if (a_async) {
 #pragma unroll
-      for (int j = 0; j < RM_GROUPS; ++j) {
-        const int c = col0 + j * 64 + g * 8;  // N % 8 == 0: a chunk is inside the row or entirely outside
-        wv[j][q] = (ok && c < N) ? ld_stream16(wrow + c) : zero;
+      for (int i = 0; i < NTM; ++i) {
+        const int q = lane + 32 * i, b = q >> 1, half = q & 1;
+        const int k0 = r0 + half * 8;
+        int bytes = (nrows - k0) * 2;
+        bytes = (b < B) ? max(0, min(16, bytes)) : 0;
+        const __half *src = bytes > 0 ? X + (size_t)b * M + m_begin + k0 : X;
+        cp_async16_zfill(dst + RM_W_BYTES + (uint32_t)b * RM_A_PITCH + (uint32_t)half * 16, src, bytes);
       }
     }
-    // A fragments: x[b, m0 + k .. + 1] for b = tile*16 + g (a0, a2) and + 8 (a1, a3), k = 2t (a0, a1), 2t + 8 (a2, a3)
-    uint32_t a[NTM][4];
+    cp_async_commit();
+  };
+  // A fragments straight from x (when the 16-byte copies are not possible): x[b, m0 + k .. + 1] for
+  // b = tile*16 + g (a0, a2) and + 8 (a1, a3), k = 2t (a0, a1), 2t + 8 (a2, a3)
+  auto load_a = [&](int m0, uint32_t (&a)[NTM][4]) {
 #pragma unroll
     for (int mt = 0; mt < NTM; ++mt) {
 #pragma unroll
       for (int f = 0; f < 4; ++f) {
         const int b = mt * 16 + g + (f & 1) * 8;
         const int k = m0 + 2 * t + (f >> 1) * 8;
-        uint32_t lo = 0, hi = 0;
-        if (b < B) {
-          if (k < m_end) lo = Xh[(size_t)b * M + k];
-          if (k + 1 < m_end) hi = Xh[(size_t)b * M + k + 1];
+        uint32_t v = 0;
+        if (b < B && k < m_end) {
+          v = Xh[(size_t)b * M + k];
+          if (k + 1 < m_end) v |= (uint32_t)Xh[(size_t)b * M + k + 1] << 16;
         }
-        a[mt][f] = lo | (hi << 16);
+        a[mt][f] = v;
       }
     }
-#pragma unroll
-    for (int j = 0; j < RM_GROUPS; ++j) {
-      const uint32_t r0[4] = {wv[j][0].x, wv[j][0].y, wv[j][0].z, wv[j][0].w};
-      const uint32_t r1[4] = {wv[j][1].x, wv[j][1].y, wv[j][1].z, wv[j][1].w};
-      const uint32_t r2[4] = {wv[j][2].x, wv[j][2].y, wv[j][2].z, wv[j][2].w};
-      const uint32_t r3[4] = {wv[j][3].x, wv[j][3].y, wv[j][3].z, wv[j][3].w};
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const uint32_t b0 = (e & 1) ? pair_hi(r0[e / 2], r1[e / 2]) : pair_lo(r0[e / 2], r1[e / 2]);
-        const uint32_t b1 = (e & 1) ? pair_hi(r2[e / 2], r3[e / 2]) : pair_lo(r2[e / 2], r3[e / 2]);
-#pragma unroll
-        for (int mt = 0; mt < NTM; ++mt)
-          mma_m16n8k16(acc[mt][j][e], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
-      }
-    }
-  }
+  };
 
-  // acc[mt][j][e][c]: activation row mt*16 + g (c 0,1) or + 8 (c 2,3); column col0 + j*64 + n*8 + e, n = 2t (c 0,2) or 2t+1
-  auto column = [&](int j, int e, int c) { return col0 + j * 64 + (2 * t + (c & 1)) * 8 + e; };
-  auto brow = [&](int mt, int c) { return mt * 16 + g + (c >> 1) * 8; };
-  if (RS == 1) {
+  // prologue: steps 0 .. D-2 in flight (a commit group per step, empty of data past the last step)
 #pragma unroll
-    for (int mt = 0; mt < NTM; ++mt)
+  for (int j = 0; j < D - 1; ++j) issue(j);
+  // ldmatrix addresses. B fragments: lane l -> row l % 16 of the step, columns (l / 16) * 8 .. + 7 of a pair of
+  // tiles. A fragments: matrix i = l / 8 -> activation rows (i & 1) * 8 + l % 8, k (i / 2) * 8 .. + 7.
+  const uint32_t ldb_off = (uint32_t)(lane & 15) * RM_PITCH + (uint32_t)(lane >> 4) * 16;
+  const uint32_t lda_off =
+      RM_W_BYTES + (uint32_t)(((lane >> 3) & 1) * 8 + (lane & 7)) * RM_A_PITCH + (uint32_t)(lane >> 4) * 16;
+  for (int s = 0; s < nsteps; ++s) {
+    cp_async_wait<D - 2>();  // this lane's copies of step s have landed ...
+    __syncwarp();            // ... and so have the other lanes'; all lanes are done reading step s - 1
+    issue(s + D - 1);        // into the stage step s - 1 used
+    const uint32_t stage = ring + (uint32_t)(s % D) * ST;
+    uint32_t a[NTM][4];
+    if (a_async) {
 #pragma unroll
-      for (int j = 0; j < RM_GROUPS; ++j)
+      for (int mt = 0; mt < NTM; ++mt) ldmatrix_x4(a[mt], stage + lda_off + (uint32_t)mt * 16 * RM_A_PITCH);
+    } else {
+      load_a(m_begin + s * 16, a);
+    }
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
+    for (int p = 0; p < RM_NT / 2; ++p) {
+      uint32_t bf[4];  // b0, b1 of tile 2p; b0, b1 of tile 2p + 1
+      ldmatrix_x4_trans(bf, stage + ldb_off + (uint32_t)p * 32);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int b = brow(mt, c), n = column(j, e, c);
-            if (b < B && n < N)
-              Y[(size_t)b * N + n] = __float2half_rn(acc[mt][j][e][c] + (bias ? __half2float(bias[n]) : 0.f));
-          }
-    return;
+      for (int mt = 0; mt < NTM; ++mt) {
+        mma_m16n8k16(acc[mt][2 * p], a[mt][0], a[mt][1], a[mt][2], a[mt][3], bf[0], bf[1]);
+        mma_m16n8k16(acc[mt][2 * p + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], bf[2], bf[3]);
+      }
+    }
   }
+  cp_async_wait<0>();
+
+  // acc[mt][nt][c]: activation row mt*16 + g (c 0,1) or + 8 (c 2,3); columns col0 + nt*8 + 2t, + 1 (c & 1)
 #pragma unroll
   for (int mt = 0; mt < NTM; ++mt)
 #pragma unroll
-    for (int j = 0; j < RM_GROUPS; ++j)
+    for (int nt = 0; nt < RM_NT; ++nt)
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int b = brow(mt, c), n = column(j, e, c);
-          if (b < B && n < N) __stcg(partial + ((size_t)rs * B + b) * N + n, acc[mt][j][e][c]);
+      for (int hp = 0; hp < 2; ++hp) {
+        const int b = mt * 16 + g + hp * 8, n = col0 + nt * 8 + 2 * t;  // n even, N even: the pair is inside or outside
+        if (b >= B || n >= N) continue;
+        float v0 = acc[mt][nt][2 * hp], v1 = acc[mt][nt][2 * hp + 1];
+        if (RS == 1) {
+          if (bias != nullptr) {
+            const float2 bb = __half22float2(*reinterpret_cast<const __half2 *>(bias + n));
+            v0 += bb.x;
+            v1 += bb.y;
+          }
+          *reinterpret_cast<__half2 *>(Y + (size_t)b * N + n) = __floats2half2_rn(v0, v1);
+        } else {
+          __stcg(reinterpret_cast<float2 *>(partial + ((size_t)rs * B + b) * N + n), make_float2(v0, v1));
         }
+      }
 }
 
 // y[b, n] = sum over the row blocks of partial[k][b][n] + bias[n], in block order (deterministic); a thread takes 8
@@ -185,12 +253,16 @@ struct RowaxpyMmaPlan {
 
 inline RowaxpyMmaPlan plan_rowaxpy_mma(int M, int N) {
   const int tiles = ceil_div(N, RM_BCOLS);
-  // about two blocks per multiprocessor, at least 64 rows per block, rows in steps of 16
-  int rs = ceil_div(2 * sm_count(), tiles);
-  const int max_rs = M / 64 > 1 ? M / 64 : 1;
+  // One block per multiprocessor (the rings of its 8 warps fill the shared memory), at least 32 rows per
+  // block, rows in steps of 16. Few row blocks also keep the fp32 partial sums (rs * B * N * 4 bytes, written and
+  // read once) small beside the gathered rows (M * N * 2 bytes).
+  int rs = sm_count() / tiles;
+  const int max_rs = M / 32 > 1 ? M / 32 : 1;
   if (rs > max_rs) rs = max_rs;
   if (rs < 1) rs = 1;
-  int rpb = ceil_div(ceil_div(M, rs), 16) * 16;
+  const int min_rs = ceil_div(M, RM_MAX_ROWS);
+  if (rs < min_rs) rs = min_rs;
+  int rpb = ceil_div(ceil_div(M, rs), 16) * 16;  // <= RM_MAX_ROWS (a multiple of 16)
   rs = ceil_div(M, rpb);
   return {tiles, rs, rpb};
 }
@@ -206,12 +278,23 @@ inline int rowaxpy_mma(int B, __half *Y, const __half *W, const __half *X, const
   const RowaxpyMmaPlan p = plan_rowaxpy_mma(M, N);
   float *partial = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + 4096);  // (header: other kernels' counters)
   const dim3 grid(p.tiles, p.rs);
+  constexpr size_t smem1 = RmSmem<1, RM_DEPTH1>::BYTES, smem2 = RmSmem<2, RM_DEPTH2>::BYTES;
+  static_assert(smem1 <= 227 * 1024 && smem2 <= 227 * 1024, "shared memory of a block");
+  static const int prepared = [] {
+    cudaError_t e1 = cudaFuncSetAttribute(rowaxpy_mma_kernel<1, RM_DEPTH1>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    cudaError_t e2 = cudaFuncSetAttribute(rowaxpy_mma_kernel<2, RM_DEPTH2>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) cudaGetLastError();
+    return (e1 == cudaSuccess && e2 == cudaSuccess) ? 0 : 1;
+  }();
+  if (prepared != 0) return DJV_ERR_CUDA;
   if (B <= 16)
-    djv::launch_kernel(rowaxpy_mma_kernel<1>, grid, dim3(RM_THREADS), 0, st, Y, W, X, idx, bias, partial, M, N, ldw,
-                       idx64, B, p.rows_per_block);
+    djv::launch_kernel(rowaxpy_mma_kernel<1, RM_DEPTH1>, grid, dim3(RM_THREADS), smem1, st, Y, W, X, idx, bias,
+                       partial, M, N, ldw, idx64, B, p.rows_per_block);
   else
-    djv::launch_kernel(rowaxpy_mma_kernel<2>, grid, dim3(RM_THREADS), 0, st, Y, W, X, idx, bias, partial, M, N, ldw,
-                       idx64, B, p.rows_per_block);
+    djv::launch_kernel(rowaxpy_mma_kernel<2, RM_DEPTH2>, grid, dim3(RM_THREADS), smem2, st, Y, W, X, idx, bias,
+                       partial, M, N, ldw, idx64, B, p.rows_per_block);
   count_launch();
   if (p.rs > 1) {
     djv::launch_kernel(rowaxpy_mma_reduce_kernel, dim3(ceil_div(B * (N / 8), 256)), dim3(256), 0, st, Y,

@@ -1,7 +1,7 @@
 """Small single-kernel cases for profiler captures and the phase trace of the one-pass MLP kernel.
 
     python -m dejavu_b200.profile_cases <case>
-        case: qkv | out_proj | attn | topk | exchange | ring | fc1 | fc2 | ring_trace
+        case: qkv | out_proj | attn | topk | exchange | ring | fc1 | fc2 | fc1_b16 | fc2_b16 | ring_trace
 
 Every case launches ONE kind of kernel a dozen times at the per-rank shapes of an OPT-175B layer under 8-way
 tensor parallelism (d 12288, 12 local heads of which 4 are active, 512 of 6144 ffn rows), rotating several weight
@@ -62,6 +62,15 @@ def main(case: str) -> None:
                 if case in ("ring", "ring_trace"): ops.mlp_sparse(x, W1[i], W2[i], idxs[i], b1, b2, fused=True)
                 elif case == "fc1": ops.gather_gemv(x, W1[i], idxs[i], b1, "relu")
                 else: ops.gather_transposed_gemv(h, W2[i], idxs[i], b2)
+    elif case in ("fc1_b16", "fc2_b16"):  # the tensor-core kernels: 16 activation rows, 4096 of 6144 rows
+        Z, K, Bt = 6144, 4096, 16
+        Ws = [rnd(Z, d) for _ in range(4)]; b1 = rnd(Z); b2 = rnd(d)
+        x = rnd(Bt, d, std=1.0); h = torch.relu(rnd(Bt, K, std=1.0))
+        idxs = [torch.randperm(Z, device=dev, generator=g)[:K].int() for _ in range(4)]
+        for _ in range(REP):
+            for i in range(4):
+                if case == "fc1_b16": ops.gather_gemv(x, Ws[i], idxs[i], b1, "relu")
+                else: ops.gather_transposed_gemv(h, Ws[i], idxs[i], b2)
     torch.cuda.synchronize()
     if case == "ring_trace":
         lib = _lib.load()
