@@ -131,9 +131,9 @@ extern "C" int djv_comm_create(djv_comm **out, int rank, int world, void *const 
   c->bufs_dev = nullptr;
   c->ctl_dev = nullptr;
   cudaError_t e = cudaMalloc(&c->bufs_dev, sizeof(void *) * AR_MAX_WORLD);
-  if (e == cudaSuccess) e = cudaMalloc(&c->ctl_dev, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMalloc(&c->ctl_dev, AR_CTL_WORDS * sizeof(unsigned));
   if (e == cudaSuccess) e = cudaMemcpy(c->bufs_dev, bufs, sizeof(void *) * world, cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = cudaMemset(c->ctl_dev, 0, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(c->ctl_dev, 0, AR_CTL_WORDS * sizeof(unsigned));
   if (e == cudaSuccess) {
     fill_sentinel_kernel<<<64, 256>>>(static_cast<uint4 *>(bufs[rank]), djv_comm_buffer_bytes(world, slot_bytes) / 16);
     e = cudaGetLastError();

@@ -185,15 +185,22 @@ __device__ __forceinline__ bool exchange_fold(const FoldArgs &a, const FoldCtx &
       }
     }
   }
-  // 2. the slot used two exchanges ago becomes free again (all pieces, whole extent)
+  // 2. the slot used two exchanges ago becomes free again: every piece, over the bytes its last exchange wrote
+  //    (ctl[AR_CTL_EXTENT + slot], recorded by that exchange's refilling consumer, which ran earlier on this stream;
+  //    the buffers start out all-sentinel, the records at 0). Not the whole slot: slots sized for a large batch
+  //    would cost every single-row exchange megabytes of stores.
   if (a.refill && refill_n > 0 && !dead) {
-    const size_t old_off = (size_t)((slot + 2) % AR_SLOTS) * a.world * a.slot_bytes;
-    const size_t n16 = (size_t)a.world * a.slot_bytes / 16;
+    const int old_slot = (slot + 2) % AR_SLOTS;
+    size_t ext = a.ctl[AR_CTL_EXTENT + old_slot];
+    ext = ext < a.slot_bytes ? ext : a.slot_bytes;
+    const size_t p16 = ext / 16, n16 = (size_t)a.world * p16;
     const size_t per = (n16 + refill_n - 1) / refill_n;
     const size_t lo = (size_t)refill_w * per, hi = (lo + per < n16) ? lo + per : n16;
     const uint4 s = make_uint4(AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2, AR_SENTINEL2);
-    uint4 *old = reinterpret_cast<uint4 *>(local + old_off);
-    for (size_t c = lo + tid; c < hi; c += THREADS) old[c] = s;
+    char *old = local + (size_t)old_slot * a.world * a.slot_bytes;
+    for (size_t c = lo + tid; c < hi; c += THREADS)
+      *reinterpret_cast<uint4 *>(old + (c / p16) * a.slot_bytes + (c % p16) * 16) = s;
+    if (refill_w == 0 && tid == 0) a.ctl[AR_CTL_EXTENT + slot] = (unsigned)((size_t)a.B * a.d * 2);
   }
 
   // 3. wait for the chunks of every piece, reduce in rank order, residual add. With few chunks per thread the

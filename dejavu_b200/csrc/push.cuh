@@ -11,7 +11,8 @@ struct djv_comm {
   size_t slot_bytes;
   // device-side tables (cudaMalloc'ed by djv_comm_create)
   void **bufs_dev;
-  unsigned *ctl_dev;  // [0] exchanges completed in earlier steps (advanced by djv_comm_end_step), [1] status
+  unsigned *ctl_dev;  // [0] exchanges completed in earlier steps (advanced by djv_comm_end_step), [1] status,
+                      // [AR_CTL_EXTENT + slot] bytes per piece the slot's last exchange wrote
   cudaStream_t last_stream;
 };
 
@@ -26,6 +27,8 @@ constexpr int AR_MAX_WORLD = 8;
 // kernel ended. Slots (e + 1) % 4 and (e + 3) % 4 are left alone: peers may already be filling the first and a
 // side stream may still be reading the second.
 constexpr int AR_SLOTS = 4;
+constexpr int AR_CTL_EXTENT = 4;  // first of the AR_SLOTS per-slot extent records in the control words
+constexpr int AR_CTL_WORDS = AR_CTL_EXTENT + AR_SLOTS;
 constexpr unsigned AR_SENTINEL2 = 0x80008000u;  // two fp16 -0.0
 
 // where a kernel sends its part of the partial sum; bufs == nullptr: nowhere (plain output)

@@ -28,8 +28,10 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
 }
 
 // Short index lists: M / 16 blocks would leave most of the device idle, so the reduction dimension is also split
-// over the blocks of a thread-block cluster (grid (tiles, S), cluster (1, S)): block s of a cluster takes k-blocks
-// s*8 + warp, then strides by 8*S; block 0 adds the others' sums through distributed shared memory, in block order.
+// over the blocks of a thread-block cluster (grid (tiles, S), cluster (1, S), 1 <= S <= 8): block s of a cluster
+// takes k-blocks s*8 + warp, then strides by 8*S; block 0 adds the others' sums through distributed shared memory, in block order.
+// (Several 16-row tiles per block, to read the activations once for all of them, was measured 2-3 times slower at
+// 16 and 32 activation rows: fewer, fatter blocks keep fewer loads in flight.)
 template <int NT, int ACT>  // NT groups of 8 activation rows
 __global__ void __launch_bounds__(MM_THREADS)
 rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
@@ -127,10 +129,28 @@ template <int NT>
 inline int launch_rowdot_mma(int act, __half *Y, const __half *W, const __half *X, const void *idx,
                              const __half *bias, int M, int N, long long ldw, int idx64, int B, cudaStream_t st) {
   const int tiles = ceil_div(M, MM_ROWS);
-  // split the reduction over 2, 4 or 8 blocks while that still leaves less than two blocks per multiprocessor
-  // and every block at least 8 k-blocks of 32
+  // Split the reduction over S <= 8 blocks (a cluster) when the tiles alone leave multiprocessors idle: the S that
+  // needs the fewest waves of resident blocks per unit of split, every warp keeping at least 8 k-blocks of 32.
+  static const int bps = [] {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rowdot_mma_kernel<NT, DJV_ACT_RELU>, MM_THREADS, 0) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      n = 1;
+    }
+    return n < 1 ? 1 : n;
+  }();
+  const int slots = sm_count() * bps;
   int S = 1;
-  while (S < 8 && tiles * S * 2 <= 2 * sm_count() && (N + 31) / 32 >= MM_WARPS * S * 2 * 8) S *= 2;
+  double best = 1e30;
+  for (int c = 1; c <= 8; ++c) {
+    if (c > 1 && (N + 31) / 32 < MM_WARPS * c * 8) break;
+    const double cost = (double)ceil_div(tiles * c, slots) / c + 0.02 * c;  // (small price per extra block summed)
+    if (cost < best - 1e-9) {
+      best = cost;
+      S = c;
+    }
+  }
   const dim3 grid(tiles, S), cluster(1, S, 1);
 #define DJV_MM(ACT_)                                                                                              \
   djv::launch_kernel_cluster(rowdot_mma_kernel<NT, ACT_>, grid, dim3(MM_THREADS), 0, st, cluster, Y, W, X, idx, bias, \

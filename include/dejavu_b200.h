@@ -91,7 +91,9 @@ int djv_gather_gemv(void *y, const void *w, const void *x, const void *idx, cons
  * Gather transposed GEMV (fc2):  y[b,n] = sum_m w[idx[m],n] * x[b,m] + bias[n].
  * Replaces gather_transposed_gemv, Dejavu/src/ops/triton/gather_gemv.py:572-644 (both its
  * atomic-add and its deterministic kernel, :432-569 and :263-425). Deterministic: partial sums over
- * fixed row chunks are written to scratch and combined in a fixed order by the last block to finish.
+ * fixed row chunks are written to scratch and combined in a fixed order (B <= 4: by the last block to finish;
+ * 5 <= B <= 32: tensor-core kernel, one pass over the gathered rows whatever B is, then a small second kernel
+ * that adds the row chunks).
  *   y (B,N) fp16 | w (Z,N) stride ldw = W2 transposed | x (B,M) | idx (M,) or NULL | bias (N,) or NULL.
  *   scratch: at least djv_gather_transposed_gemv_scratch_bytes(B,N,M) bytes, 256-byte aligned, and its
  *   first 4096 bytes must be ZERO before the first call (the kernel leaves them zero again).
@@ -165,6 +167,8 @@ int djv_mlp_sparse_fused(void *y, const void *w1, const void *w2t, const void *x
  * Rule: the K largest scores; ties on the K-th score go to the LOWEST indices; NaN ranks above +inf.
  * Output: K indices in ascending index order, written as int32 to idx32 and/or int64 to idx64
  * (either may be NULL). scores: fp16 (score_is_f32 = 0) or fp32. 0 <= K <= n, n*elemsize <= 200 KiB.
+ * n >= 4096 runs as a cluster of 8 blocks (each holds an eighth of the keys), shorter vectors as one block;
+ * both give the same index list.
  * ------------------------------------------------------------------------------------------- */
 int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int n, int K, int score_is_f32,
              void *stream);

@@ -87,6 +87,11 @@ GATHER_CASES = [
     (6144, 12288, 100, 9, "rand64"),
     (2048, 1000, 300, 24, "rand32"),   # row length not a multiple of 32
     (4608, 9216, 77, 32, "dup32"),
+    (6144, 2048, 5000, 12, "rand32"),  # long lists: several 16-row tiles per block (fc1), many ring steps (fc2)
+    (6144, 1024, 4800, 32, "rand32"),
+    (6144, 1024, 4805, 20, "rand64"),  # ragged last tile; activations not 16-byte aligned per row
+    (2048, 1000, 304, 24, "sorted32"), # last column tile partly outside the rows
+    (8192, 512, 2500, 5, "dup64"),
 ]
 
 
@@ -443,12 +448,16 @@ def _no_neg_zero(t):
     return t
 
 
-@pytest.mark.parametrize("world,B,d", [(2, 1, 9216), (4, 2, 1024), (8, 1, 12288), (1, 3, 256), (2, 1, 20480)])
-def test_allreduce_push_protocol_single_gpu(cuda, world, B, d):
+@pytest.mark.parametrize("world,B,d,slack", [(2, 1, 9216, 1), (4, 2, 1024, 1), (8, 1, 12288, 1), (1, 3, 256, 1),
+                                             (2, 1, 20480, 1), (8, 4, 12288, 4), (2, 3, 1024, 2)])
+def test_allreduce_push_protocol_single_gpu(cuda, world, B, d, slack):
+    """slack > 1: slots larger than an exchange needs, and the number of rows changes from step to step (the refill
+    covers what the slot's last exchange wrote, not the whole slot)."""
     from dejavu_b200 import _lib
 
     lib = _lib.load()
-    slot_bytes = (B * d * 2 + 255) // 256 * 256
+    B_max = B
+    slot_bytes = (B_max * d * 2 + 255) // 256 * 256 * slack
     comm, bufs_t = _make_comm(lib, cuda, world, slot_bytes)
     own = bufs_t[0].view(SLOTS, world, slot_bytes // 2)
     assert bool((own == SENT).all()), "comm_create fills the rank's own buffer with the sentinel"
@@ -457,6 +466,7 @@ def test_allreduce_push_protocol_single_gpu(cuda, world, B, d):
     st = torch.cuda.current_stream().cuda_stream
     e = 0  # exchanges so far; steps of 3 exchanges each, so that the slot sequence wraps inside a step
     for step in range(4):
+        B = B_max if (slack == 1 or step % 2 == 0) else 1
         for seq in range(3):
             parts = rand(gen, (world, B, d))
             parts[:, :, :3] = -0.0  # the sentinel value inside real data
