@@ -32,8 +32,16 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
 // takes k-blocks s*8 + warp, then strides by 8*S; block 0 adds the others' sums through distributed shared memory, in block order.
 // (Several 16-row tiles per block, to read the activations once for all of them, was measured 2-3 times slower at
 // 16 and 32 activation rows: fewer, fatter blocks keep fewer loads in flight.)
+// Blocks per multiprocessor the kernel is compiled for: a block's fixed costs (row numbers, first loads, the
+// reduction at the end) overlap with other resident blocks' streaming, so more blocks of fewer registers per
+// thread beat 4 blocks with deeper per-warp load pipelines (measured: K = 6144, 8 activation rows, 30 us against 42).
+template <int NT>
+struct MmaBlocks {
+  static constexpr int PER_SM = NT == 1 ? 5 : 1;  // (1: whatever the compiler's register count allows, 4 here)
+};
+
 template <int NT, int ACT>  // NT groups of 8 activation rows
-__global__ void __launch_bounds__(MM_THREADS)
+__global__ void __launch_bounds__(MM_THREADS, MmaBlocks<NT>::PER_SM)
 rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __half *__restrict__ X,
                   const void *__restrict__ idx, const __half *__restrict__ bias, int M, int N,
                   long long ldw, int idx64, int B) {
@@ -58,7 +66,7 @@ rowdot_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const __
 
   const int kblocks = (N + 31) / 32;
   // weight and activation loads of U k-blocks are all issued before the first MMA needs them
-  constexpr int U = (NT <= 2) ? 4 : 2;
+  constexpr int U = 2;
   for (int kb0 = sblk * MM_WARPS + warp; kb0 < kblocks; kb0 += MM_WARPS * S * U) {
     uint4 a_lo[U], a_hi[U], xv[U][NT];
 #pragma unroll
@@ -129,8 +137,7 @@ template <int NT>
 inline int launch_rowdot_mma(int act, __half *Y, const __half *W, const __half *X, const void *idx,
                              const __half *bias, int M, int N, long long ldw, int idx64, int B, cudaStream_t st) {
   const int tiles = ceil_div(M, MM_ROWS);
-  // Split the reduction over S <= 8 blocks (a cluster) when the tiles alone leave multiprocessors idle: the S that
-  // needs the fewest waves of resident blocks per unit of split, every warp keeping at least 8 k-blocks of 32.
+  // Split the reduction over the S blocks of a cluster when the tiles alone leave multiprocessors idle.
   static const int bps = [] {
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rowdot_mma_kernel<NT, DJV_ACT_RELU>, MM_THREADS, 0) !=
@@ -141,16 +148,30 @@ inline int launch_rowdot_mma(int act, __half *Y, const __half *W, const __half *
     return n < 1 ? 1 : n;
   }();
   const int slots = sm_count() * bps;
+  // Measured behaviour: the resident blocks run in waves; a wave costs a fixed ~5 us (row numbers, first loads,
+  // reduction, cluster barriers) plus, per k-block of 32 columns a warp walks, the larger of a latency floor that
+  // grows with the activation rows and the wave's bytes per k-block step (8 KB per block) over the HBM rate.
+  // S in {1, 2, 4, 8} (other cluster sizes measured slower than either neighbour), every warp keeps >= 4 k-blocks.
+  const int kblocks = (N + 31) / 32;
   int S = 1;
   double best = 1e30;
-  for (int c = 1; c <= 8; ++c) {
-    if (c > 1 && (N + 31) / 32 < MM_WARPS * c * 8) break;
-    const double cost = (double)ceil_div(tiles * c, slots) / c + 0.02 * c;  // (small price per extra block summed)
-    if (cost < best - 1e-9) {
-      best = cost;
+  for (int c = 1; c <= 8; c *= 2) {
+    if (c > 1 && kblocks < MM_WARPS * c * 4) break;
+    const double kb_per_warp = (double)ceil_div(kblocks, MM_WARPS * c);
+    const double floor_us = 0.6 + 0.23 * NT;
+    double t = 0.0;
+    for (int left = tiles * c; left > 0; left -= slots) {
+      const int nb = left < slots ? left : slots;
+      const double bw_us = nb * 8192.0 / 6.5e6;
+      t += 5.0 + kb_per_warp * (floor_us > bw_us ? floor_us : bw_us);
+    }
+    if (t < best - 1e-9) {
+      best = t;
       S = c;
     }
   }
+  static const int k_s = env_int("DJV_MMA_S", 0);  // development knob
+  if (k_s >= 1 && k_s <= 8) S = k_s;
   const dim3 grid(tiles, S), cluster(1, S, 1);
 #define DJV_MM(ACT_)                                                                                              \
   djv::launch_kernel_cluster(rowdot_mma_kernel<NT, ACT_>, grid, dim3(MM_THREADS), 0, st, cluster, Y, W, X, idx, bias, \
