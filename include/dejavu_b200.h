@@ -166,9 +166,9 @@ int djv_mlp_sparse_fused(void *y, const void *w1, const void *w2t, const void *x
  * Dejavu/src/models/modules/mha_dejavu.py:1069, 1369, 1506-1507.
  * Rule: the K largest scores; ties on the K-th score go to the LOWEST indices; NaN ranks above +inf.
  * Output: K indices in ascending index order, written as int32 to idx32 and/or int64 to idx64
- * (either may be NULL). scores: fp16 (score_is_f32 = 0) or fp32. 0 <= K <= n, n*elemsize <= 200 KiB.
- * n >= 4096 runs as a cluster of 8 blocks (each holds an eighth of the keys), shorter vectors as one block;
- * both give the same index list.
+ * (either may be NULL). scores: fp16 (score_is_f32 = 0) or fp32. 0 <= K <= n, n*elemsize <= 1600 KiB
+ * (DJV_ERR_UNSUPPORTED above). n >= 4096 runs as a cluster of 8 blocks (each holds an eighth of the keys in its
+ * shared memory), shorter vectors as one block; both give the same index list.
  * ------------------------------------------------------------------------------------------- */
 int djv_topk(int32_t *idx32, int64_t *idx64, const void *scores, int n, int K, int score_is_f32,
              void *stream);

@@ -60,7 +60,7 @@ def test_argument_validation_happens_before_any_launch(lib):
     assert rc == _lib.ERR_INVALID and b"null" in lib.djv_last_error()
     rc = lib.djv_topk(fake, None, fake, 10, 11, 0, None)  # K > n
     assert rc == _lib.ERR_INVALID
-    rc = lib.djv_topk(fake, None, fake, 200000, 5, 0, None)  # too large for one block
+    rc = lib.djv_topk(fake, None, fake, 1000000, 5, 0, None)  # too large for the shared memory of 8 blocks
     assert rc == _lib.ERR_UNSUPPORTED
     rc = lib.djv_qkv_proj_sparse(fake, fake, fake, fake, fake, None, 17, 256, 4, 64, 2, None)  # 17 rows
     assert rc == _lib.ERR_INVALID

@@ -240,7 +240,8 @@ def test_outputs_stay_inside_their_buffers(cuda):
 # top-K
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("n,k", [(1, 1), (12, 4), (96, 32), (1000, 0), (1000, 1000), (4608, 512), (16384, 2048),
-                                 (36864, 4096), (49152, 6144), (50272, 1)])
+                                 (36864, 4096), (49152, 6144), (50272, 1), (4096, 4096), (4100, 7), (4099, 0),
+                                 (200000, 5000)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_topk_exact_index_sets(cuda, n, k, dtype):
     from dejavu_b200 import ops
@@ -262,6 +263,14 @@ def test_topk_special_values(cuda):
     s = torch.tensor([1.0, float("inf"), -0.0, 0.0, float("nan"), -float("inf"), 3.0, 3.0, -2.0], dtype=torch.float16)
     for k in range(0, 10):
         assert ops.topk_indices(s.to(cuda), k, torch.int32).cpu().tolist() == O.topk_indices(s, k).tolist()
+    # the same special values inside a vector long enough for the cluster kernel, spread over its blocks
+    gen = torch.Generator().manual_seed(3)
+    long = torch.randn(6000, generator=gen).half()
+    for i, v in enumerate(s.tolist()):
+        long[(i * 677) % 6000] = v
+    long[5999] = float("nan")
+    for k in (1, 2, 3, 5, 2999, 5998, 6000):
+        assert ops.topk_indices(long.to(cuda), k, torch.int32).cpu().tolist() == O.topk_indices_fast(long, k).tolist()
     s2 = torch.randn(300).half()
     got = ops.topk_indices(s2.to(cuda), 50, torch.int64).cpu()
     rest = torch.ones(300, dtype=torch.bool)
