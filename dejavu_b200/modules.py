@@ -45,8 +45,8 @@ PUSH_PARTIALS = os.environ.get("DJV_PUSH_PARTIALS", "1") != "0"
 # kernels whose index list is known to be complete prefetch weights before their PDL wait (development knob)
 EARLY_PREFETCH = os.environ.get("DJV_EARLY_PREFETCH", "1") != "0"
 # with a comm: exchange + residual + LayerNorm + fc1 + ReLU + fc2 (+ send) of a block in one kernel. "0" (default):
-# off, the separate kernels measured faster at every tensor-parallel degree (OPT-175B TP8: 5.18 against 6.25
-# ms/token, OPT-66B TP8: 3.06 against 3.15); "1": on wherever the shape allows; "auto": on for a real
+# off, the separate kernels measured faster at every tensor-parallel degree (OPT-66B TP8: 3.06 against 3.15
+# ms/token; 16 layers of an OPT-175B TP8 shard on one GPU: 0.94 against 1.04 ms); "1": on wherever the shape allows; "auto": on for a real
 # tensor-parallel group when the shard's index list is short enough to be in flight at once
 FUSED_MLP = os.environ.get("DJV_FUSED_MLP", "0")
 # where the main stream joins the side stream that selects this layer's MLP rows: "attend" = before the attention
@@ -58,6 +58,11 @@ MLP_IDX_JOIN = os.environ.get("DJV_MLP_IDX_JOIN", "attend")
 # the weights a rank gathers per layer stay below DJV_L2_PREFETCH_MB (development knob)
 L2_PREFETCH = os.environ.get("DJV_L2_PREFETCH", "0")
 L2_PREFETCH_MB = float(os.environ.get("DJV_L2_PREFETCH_MB", "100"))
+# batch >= 4: the per-sequence attention chains of sequences 1.. run on up to this many extra streams (branches of
+# the captured graph), at least two sequences per stream, once sequence 0 has brought the selected heads' weights
+# into L2; 0 = all on the main stream. Measured on OPT-6.7B, one GPU, ms per step without / with: batch 8 7.95 /
+# 5.65, batch 16 16.9 / 8.4; one sequence per stream (batch 4 on 3 streams) was slower than none (4.9 / 4.7).
+BATCH_STREAMS = int(os.environ.get("DJV_BATCH_STREAMS", "8"))
 _SIDE_STREAMS: dict = {}
 _SIDE_DIRTY: dict = {}  # device index -> names of side streams forked since the last join
 
@@ -67,6 +72,15 @@ def side_streams(device) -> dict:
     if key not in _SIDE_STREAMS:
         _SIDE_STREAMS[key] = {"att": torch.cuda.Stream(device=device), "mlp": torch.cuda.Stream(device=device)}
     return _SIDE_STREAMS[key]
+
+
+def batch_streams(device, n) -> list:
+    """The first n of the streams that carry the attention chains of sequences 1.. of a batch."""
+    streams = side_streams(device)
+    for j in range(n):
+        if f"batch{j}" not in streams:
+            streams[f"batch{j}"] = torch.cuda.Stream(device=device)
+    return [streams[f"batch{j}"] for j in range(n)]
 
 
 class _side:
@@ -481,14 +495,14 @@ class ParallelMHASparseAttMlp(nn.Module):
         """One decode step of this layer's attention; `between()` is called after the projection kernels are
         queued and before the attention kernel (the place to fork look-ahead work onto a side stream).
         A batch runs sequence by sequence through the same kernels (each sequence has its own window and caches;
-        the head selection is shared), after the first sequence the selected heads' weights come from L2."""
+        the head selection is shared): sequence 0 on the main stream, the others, whose weights then come from L2,
+        as parallel chains on up to BATCH_STREAMS extra streams that rejoin before the result is used."""
         n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
         B = x.size(0)
         k_cache, v_cache = inference_params.key_value_memory_dict[self.layer_idx]
         assert k_cache.size(0) >= B and v_cache.size(0) >= B
         S = v_cache.shape[2]
         seqs = self._decode_buffers(x.device, S, B)
-        st = ops._stream()
         xf = x.reshape(B, d).contiguous()
         nnz = 0
         if head_idx is not None:
@@ -500,35 +514,70 @@ class ParallelMHASparseAttMlp(nn.Module):
         step_is_open = 1 if (head_idx is not None and getattr(head_idx, "_step_opened_for", None) is self) else 0
         # an opened step means the state was written on a side stream whose event the main stream has waited on
         early = EARLY_PREFETCH and step_is_open == 1 and getattr(head_idx, "_ready_event", None) is not None
-        with ops.indices_ready(early):
-            for i, b in enumerate(seqs[:B]):
-                call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
-                     None if bias is None else bias.data_ptr(), xf[i].data_ptr(), b["x_ring"].data_ptr(),
-                     k_cache[i].data_ptr(), v_cache[i].data_ptr(), b["state"].data_ptr(),
-                     None if head_idx is None else head_idx.data_ptr(), nnz, d, n, hd, S, step_is_open, st)
-        if between is not None:
-            between()
-        for i, b in enumerate(seqs[:B]):
-            call("djv_attn_step_attend", b["ctx"].data_ptr(), b["q"].data_ptr(), k_cache[i].data_ptr(),
-                 v_cache[i].data_ptr(), b["state"].data_ptr(), n, hd, S, float(self.softmax_scale),
-                 b["scratch"].data_ptr(), b["scratch"].numel(), st)
         out = torch.empty(B, d, dtype=x.dtype, device=x.device)
         ob = self.out_proj.bias
+
+        def project(i, b):
+            call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
+                 None if bias is None else bias.data_ptr(), xf[i].data_ptr(), b["x_ring"].data_ptr(),
+                 k_cache[i].data_ptr(), v_cache[i].data_ptr(), b["state"].data_ptr(),
+                 None if head_idx is None else head_idx.data_ptr(), nnz, d, n, hd, S, step_is_open, ops._stream())
+
+        def attend(i, b):
+            call("djv_attn_step_attend", b["ctx"].data_ptr(), b["q"].data_ptr(), k_cache[i].data_ptr(),
+                 v_cache[i].data_ptr(), b["state"].data_ptr(), n, hd, S, float(self.softmax_scale),
+                 b["scratch"].data_ptr(), b["scratch"].numel(), ops._stream())
+
+        def project_out(i, b):
+            state = b["state"]
+            eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
+            n_eff_ptr = state.data_ptr() + 4 * 2
+            if self.push_comm is not None and B == 1:
+                seq = self.push_comm.next_seq()
+                call("djv_out_proj_sparse_push", self.push_comm.handle, seq, self.out_proj.weight.data_ptr(),
+                     b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d,
+                     n, hd, n, ops._stream())
+                self.push_comm.note_pushed(out, seq)
+            else:
+                call("djv_out_proj_sparse", out[i].data_ptr(), self.out_proj.weight.data_ptr(),
+                     b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n,
+                     hd, n, ops._stream())
+
+        n_extra = min((B - 1) // 2, BATCH_STREAMS) if (SIDE_STREAMS_ENABLED and x.is_cuda and B >= 4) else 0
         with ops.indices_ready(early):
-            for i, b in enumerate(seqs[:B]):
-                state = b["state"]
-                eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
-                n_eff_ptr = state.data_ptr() + 4 * 2
-                if self.push_comm is not None and B == 1:
-                    seq = self.push_comm.next_seq()
-                    call("djv_out_proj_sparse_push", self.push_comm.handle, seq, self.out_proj.weight.data_ptr(),
-                         b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d,
-                         n, hd, n, st)
-                    self.push_comm.note_pushed(out, seq)
-                else:
-                    call("djv_out_proj_sparse", out[i].data_ptr(), self.out_proj.weight.data_ptr(),
-                         b["ctx"].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), 1, d, n,
-                         hd, n, st)
+            project(0, seqs[0])
+            if n_extra == 0:
+                for i in range(1, B):
+                    project(i, seqs[i])
+        joins = []
+        if n_extra > 0:
+            # Sequence 0 has pulled the selected heads' weights through L2; the other sequences' chains (projection,
+            # attention, out_proj: independent of each other) now run side by side on extra streams and hit L2.
+            main = torch.cuda.current_stream()
+            fork = torch.cuda.Event()
+            fork.record(main)
+            for j, stream in enumerate(batch_streams(x.device, n_extra)):
+                stream.wait_event(fork)
+                for t in (out, xf):
+                    t.record_stream(stream)
+                with torch.cuda.stream(stream):
+                    for i in range(1 + j, B, n_extra):
+                        project(i, seqs[i])
+                        attend(i, seqs[i])
+                        project_out(i, seqs[i])
+                    done = torch.cuda.Event()
+                    done.record(stream)
+                joins.append(done)
+        if between is not None:
+            between()
+        on_main = 1 if n_extra > 0 else B  # sequences whose chain continues on the main stream
+        for i in range(on_main):
+            attend(i, seqs[i])
+        with ops.indices_ready(early):
+            for i in range(on_main):
+                project_out(i, seqs[i])
+        for done in joins:
+            torch.cuda.current_stream().wait_event(done)
         # the window advance is folded into the next step's first kernel (no djv_attn_step_finish launch)
         return out.view(B, 1, d)
 
