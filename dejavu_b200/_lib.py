@@ -51,6 +51,8 @@ SIGNATURES = {
     "djv_attn_step_project": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "djv_topk_attn_prep": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "djv_attn_step_attend": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "djv_attn_step_project_batch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "djv_attn_step_attend_batch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "djv_attn_step_finish": (_i, [_vp, _i, _vp]),
     "djv_decode_attn_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "djv_decode_attn": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),

@@ -30,9 +30,22 @@ __global__ void attn_state_reset_kernel(int *st, int nheads, int prompt_len) {
 // Step 1 of djv_attn_step as a kernel of its own (see attn_prep_block).
 __global__ void __launch_bounds__(1024)
 attn_prep_kernel(int *__restrict__ st, const int *__restrict__ head_idx, int nnz,
-                 const __half *__restrict__ x, __half *__restrict__ x_ring, int d, int nheads, int S) {
+                 const __half *__restrict__ x, __half *__restrict__ x_ring, int d, int nheads, int S, int nseq,
+                 long long seq_ring) {
   pdl_prologue();
   attn_prep_block(st, head_idx, nnz, x, x_ring, d, nheads, S);
+  if (nseq > 1) {
+    // the other sequences of the batch share this state; each has its own window: x_ring[b][slot] = x[b]
+    __syncthreads();
+    if (st[ST_STATUS] != 0) return;
+    const int slot = st[ST_SLOT];
+    const int per = d / 8;
+    for (int c = threadIdx.x; c < (nseq - 1) * per; c += blockDim.x) {
+      const int b = 1 + c / per, k = c % per;
+      reinterpret_cast<uint4 *>(x_ring + (size_t)b * seq_ring + (size_t)slot * d)[k] =
+          reinterpret_cast<const uint4 *>(x + (size_t)b * d)[k];
+    }
+  }
 }
 
 __global__ void attn_finish_kernel(int *st) {
@@ -76,7 +89,17 @@ struct QkvArgs {
   const __half *x_cur;
   __half *x_ring_w;
   int early;  // MODE 1: the state is complete before this kernel can start; prefetch weights before the wait
+  // MODE 1 with nseq sequences that share the state (same head selection, same window): elements between two
+  // sequences' windows (x), query rows (q_out) and caches. Block (., y) takes sequences y*QKV_SEQ_GROUP ..: their
+  // token rows go through the same pass over the weight rows, 16 at a time.
+  int nseq;
+  long long seq_x, seq_q, seq_k, seq_v;
 };
+constexpr int QKV_SEQ_GROUP = 8;  // sequences per block
+// a token row of MODE 1: (sequence << 4) | window slot
+__device__ __forceinline__ int row_seq(int code) { return code >> 4; }
+__device__ __forceinline__ int row_slot(int code) { return code & (DJV_KV_WINDOW - 1); }
+static_assert(DJV_KV_WINDOW == 16, "token-row codes keep the window slot in 4 bits");
 
 // ROWS weight rows against NB token rows: every activation chunk is loaded (through L1) once and used for
 // all ROWS weight rows, so L1 traffic per weight byte is NB / ROWS. Without that sharing a head with three
@@ -142,8 +165,10 @@ __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, i
   for (int j = 0; j < NT; ++j) {
     xr[j] = nullptr;
     if (j * 8 + g < nrows) {
-      const int r = rows_s[j * 8 + g];
-      xr[j] = (MODE == 1 && a.x_cur != nullptr && r == cur_slot) ? a.x_cur : a.x + (size_t)r * a.d;
+      const int code = rows_s[j * 8 + g];
+      const int r = (MODE == 1) ? row_slot(code) : code;
+      const __half *xs = (MODE == 1) ? a.x + (size_t)row_seq(code) * a.seq_x : a.x;
+      xr[j] = (MODE == 1 && a.x_cur != nullptr && r == cur_slot) ? a.x_cur : xs + (size_t)r * a.d;
     }
   }
 
@@ -196,17 +221,19 @@ __device__ __forceinline__ void qkv_mma_rows(const QkvArgs &a, int qkv, int h, i
     const int jj = jrow0 + tl * 16 + row;
     if (a.bias) sum += __half2float(a.bias[((size_t)qkv * a.nheads + h) * a.hd + jj]);
     const __half out = __float2half_rn(sum);
-    const int trow = rows_s[tok];
+    const int code = rows_s[tok];
+    const int trow = (MODE == 1) ? row_slot(code) : code;
+    const size_t sq = (MODE == 1) ? (size_t)row_seq(code) : 0;
     if (MODE == 0) {
       a.y[(((size_t)trow * 3 + qkv) * a.nheads + h) * a.hd + jj] = out;
     } else if (qkv == 1) {
       const int pos = base + trow;
-      a.k_cache[(((size_t)h * (a.hd / 8) + jj / 8) * a.S + pos) * 8 + jj % 8] = out;
+      a.k_cache[sq * a.seq_k + (((size_t)h * (a.hd / 8) + jj / 8) * a.S + pos) * 8 + jj % 8] = out;
     } else if (qkv == 2) {
       const int pos = base + trow;
-      a.v_cache[((size_t)h * a.S + pos) * a.hd + jj] = out;
+      a.v_cache[sq * a.seq_v + ((size_t)h * a.S + pos) * a.hd + jj] = out;
     } else {
-      a.q_out[(size_t)h * a.hd + jj] = out;
+      a.q_out[sq * a.seq_q + (size_t)h * a.hd + jj] = out;
     }
   }
 }
@@ -239,7 +266,7 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int U = (ROWS == 1) ? 8 : (ROWS == 2 ? 4 : 2);  // ROWS * U = 8 weight loads in flight per lane
   __shared__ float red[QKV_WARPS][ROWS][8];
-  __shared__ int rows_s[DJV_KV_WINDOW];
+  __shared__ int rows_s[QKV_SEQ_GROUP * DJV_KV_WINDOW];
   __shared__ int nrows_s;
 
   const int jblocks = a.hd / RPB;
@@ -273,13 +300,13 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
         if (r >= 0) rows_s[n++] = r;
       }
     } else {
-      if (qkv == 0) {
-        rows_s[n++] = slot;
-      } else {
-        const unsigned m = (unsigned)st_rowmask(a.state, a.nheads)[i];
+      // the sequences of this block, sequence-major (all of them have the same pending window slots)
+      const int seq0 = blockIdx.y * QKV_SEQ_GROUP;
+      const int seq1 = min(a.nseq > 0 ? a.nseq : 1, seq0 + QKV_SEQ_GROUP);
+      const unsigned m = (qkv == 0) ? (1u << slot) : (unsigned)st_rowmask(a.state, a.nheads)[i];
+      for (int sq = seq0; sq < seq1; ++sq)
         for (int s = 0; s <= slot; ++s)
-          if (m >> s & 1u) rows_s[n++] = s;
-      }
+          if (m >> s & 1u) rows_s[n++] = (sq << 4) | s;
     }
     nrows_s = n;
   }
@@ -289,8 +316,13 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
   if constexpr (RPB >= 8) {
     // full or half tensor-core tiles; measured faster than the CUDA-core path below even for one token row
     __shared__ float red_mma[QKV_WARPS * 2 * 16 * 8];
-    if (nrows <= 8) qkv_mma_rows<MODE, RPB, 1>(a, qkv, h, jb * RPB, nrows, rows_s, base, slot, red_mma);
-    else qkv_mma_rows<MODE, RPB, 2>(a, qkv, h, jb * RPB, nrows, rows_s, base, slot, red_mma);
+    // 16 token rows per pass over the block's weight rows (one pass unless several sequences have rows pending)
+    for (int r0 = 0; r0 < nrows; r0 += 16) {
+      const int nr = min(16, nrows - r0);
+      if (r0 > 0) __syncthreads();  // the reduction buffer of the pass before has been read
+      if (nr <= 8) qkv_mma_rows<MODE, RPB, 1>(a, qkv, h, jb * RPB, nr, rows_s + r0, base, slot, red_mma);
+      else qkv_mma_rows<MODE, RPB, 2>(a, qkv, h, jb * RPB, nr, rows_s + r0, base, slot, red_mma);
+    }
     // (the CUDA-core path below is compiled for the one-row-per-block variant only)
   } else {
 
@@ -316,9 +348,11 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
     const uint4 *xp[NBMAX];
 #pragma unroll
     for (int r = 0; r < NBMAX; ++r) {
-      const int tr = rows_s[r0 + (r < nb ? r : 0)];
+      const int code = rows_s[r0 + (r < nb ? r : 0)];
+      const int tr = (MODE == 1) ? row_slot(code) : code;
+      const uint4 *xs = (MODE == 1) ? Xv + (size_t)row_seq(code) * (a.seq_x / 8) : Xv;
       xp[r] = (MODE == 1 && a.x_cur != nullptr && tr == slot) ? reinterpret_cast<const uint4 *>(a.x_cur)
-                                                              : Xv + (size_t)tr * nchunks;
+                                                              : xs + (size_t)tr * nchunks;
     }
     if (nb == 1) {
       const uint4 *x1[1] = {xp[0]};
@@ -373,17 +407,19 @@ __global__ void __launch_bounds__(QKV_THREADS, 2) qkv_sparse_kernel(QkvArgs a) {
         const int j = j0 + jr;
         for (int r = 0; r < nb; ++r) {
           const __half out = __float2half_rn(acc[jr][r] + bv[jr]);
-          const int row = rows_s[r0 + r];
+          const int code = rows_s[r0 + r];
+          const int row = (MODE == 1) ? row_slot(code) : code;
+          const size_t sq = (MODE == 1) ? (size_t)row_seq(code) : 0;
           if (MODE == 0) {
             a.y[(((size_t)row * 3 + qkv) * a.nheads + h) * a.hd + j] = out;
           } else if (qkv == 0) {
-            a.q_out[(size_t)h * a.hd + j] = out;
+            a.q_out[sq * a.seq_q + (size_t)h * a.hd + j] = out;
           } else if (qkv == 1) {
             const int pos = base + row;
-            a.k_cache[(((size_t)h * (a.hd / 8) + j / 8) * a.S + pos) * 8 + j % 8] = out;
+            a.k_cache[sq * a.seq_k + (((size_t)h * (a.hd / 8) + j / 8) * a.S + pos) * 8 + j % 8] = out;
           } else {
             const int pos = base + row;
-            a.v_cache[((size_t)h * a.S + pos) * a.hd + j] = out;
+            a.v_cache[sq * a.seq_v + ((size_t)h * a.S + pos) * a.hd + j] = out;
           }
         }
       }
@@ -705,19 +741,12 @@ __global__ void cache_copy_sparse_kernel(const __half *__restrict__ src, __half 
 
 using namespace djv;
 
-static int pick_wpr(long long rows, int nchunks) {
-  const long long target = (long long)sm_count() * 32;
-  int wpr = 1;
-  while (wpr < 8 && rows * wpr < target && nchunks >= 64 * wpr * 2) wpr *= 2;
-  return wpr;
-}
-
 // `rows` = output rows expected in a typical call (heads in use x 3 x head_dim). Blocks of 32, 16 or 8 weight
 // rows run on the tensor cores with the block's 8 warps splitting the reduction dimension; the block size is
 // the largest that still gives every multiprocessor about two blocks. Very small calls put a whole block on
 // one row.
 template <int MODE>
-static void launch_qkv(QkvArgs a, int capacity_heads, long long rows, cudaStream_t st) {
+static void launch_qkv(QkvArgs a, int capacity_heads, long long rows, cudaStream_t st, int nseq = 1) {
   const long long sms = sm_count();
   // development knob, read at every launch: DJV_QKV_RPB (32, 16, 8 or 1: force the rows-per-block variant)
   const int force = env_int("DJV_QKV_RPB", 0);
@@ -726,7 +755,8 @@ static void launch_qkv(QkvArgs a, int capacity_heads, long long rows, cudaStream
   if (a.hd % rpb != 0) rpb = 8;
 #define DJV_QKV(WPR_, ROWS_)                                                                       \
   djv::launch_kernel(qkv_sparse_kernel<MODE, WPR_, ROWS_>,                                         \
-                     capacity_heads * 3 * (a.hd / ((QKV_WARPS / WPR_) * ROWS_)), QKV_THREADS, 0, st, a)
+                     dim3(capacity_heads * 3 * (a.hd / ((QKV_WARPS / WPR_) * ROWS_)), (nseq + QKV_SEQ_GROUP - 1) / QKV_SEQ_GROUP), \
+                     QKV_THREADS, 0, st, a)
   if (rpb == 32) DJV_QKV(1, 4);
   else if (rpb == 16) DJV_QKV(2, 4);
   else if (rpb == 8) DJV_QKV(2, 2);
@@ -908,22 +938,26 @@ extern "C" size_t djv_attn_step_scratch_bytes(int nheads, int hd, int S) {
   return attn_scratch_bytes(nheads, 1, hd, S);
 }
 
-extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x,
-                                     void *x_ring, void *k_cache, void *v_cache, int32_t *state,
-                                     const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
-                                     int step_is_open, void *stream) {
+// B sequences in lockstep that share `state` (one head selection, one window position): q_out (B,nheads,hd),
+// x (B,d), x_ring (B,16,d), caches (B,...) contiguous over the batch.
+static int attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x, void *x_ring,
+                             void *k_cache, void *v_cache, int32_t *state, const int32_t *head_idx, int nnz, int d,
+                             int nheads, int hd, int S, int B, int step_is_open, void *stream) {
   DJV_REQUIRE(q_out && wqkv && x && x_ring && k_cache && v_cache && state, "attn_step: null pointer");
   int rc = check_hd("attn_step", hd, d);
   if (rc) return rc;
+  DJV_REQUIRE(B >= 1 && B <= 65535, "attn_step: batch %d outside [1,65535]", B);
   DJV_REQUIRE(nheads >= 1 && nheads <= 1024, "attn_step: nheads=%d outside [1,1024]", nheads);
   DJV_REQUIRE(head_idx == nullptr || (nnz >= 0 && nnz <= nheads), "attn_step: nnz=%d outside [0,%d]", nnz, nheads);
   DJV_REQUIRE(S >= 1, "attn_step: cache capacity S=%d", S);
   DJV_REQUIRE(aligned16(wqkv) && aligned16(x) && aligned16(x_ring) && aligned16(k_cache) && aligned16(v_cache),
               "attn_step: pointers must be 16-byte aligned");
+  DJV_REQUIRE(B == 1 || !step_is_open, "attn_step: a batch opens its step itself");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long seq_ring = (long long)DJV_KV_WINDOW * d;
   if (!step_is_open) {
     djv::launch_kernel(attn_prep_kernel, 1, 1024, 0, st, state, head_idx, head_idx ? nnz : 0,
-                       static_cast<const __half *>(x), static_cast<__half *>(x_ring), d, nheads, S);
+                       static_cast<const __half *>(x), static_cast<__half *>(x_ring), d, nheads, S, B, seq_ring);
     count_launch();
   }
   QkvArgs a{};
@@ -936,22 +970,44 @@ extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *
   a.k_cache = static_cast<__half *>(k_cache);
   a.v_cache = static_cast<__half *>(v_cache);
   a.S = S;
+  a.nseq = B;
+  a.seq_x = seq_ring;
+  a.seq_q = (long long)nheads * hd;
+  a.seq_k = (long long)nheads * hd * S;
+  a.seq_v = (long long)nheads * hd * S;
   if (step_is_open) {
     a.x_cur = static_cast<const __half *>(x);
     a.x_ring_w = static_cast<__half *>(x_ring);
     a.early = early_prefetch() ? 1 : 0;
   }
   const int typical = head_idx ? (nnz > 0 ? nnz : 1) : nheads;
-  launch_qkv<1>(a, nheads, (long long)typical * 3 * hd, st);
+  launch_qkv<1>(a, nheads, (long long)typical * 3 * hd, st, B);
   count_launch();
   return check_launch("attn_step_project");
 }
 
-extern "C" int djv_attn_step_attend(void *ctx, const void *q, const void *k_cache, const void *v_cache,
-                                    int32_t *state, int nheads, int hd, int S, float softmax_scale,
-                                    void *scratch, size_t scratch_bytes, void *stream) {
+extern "C" int djv_attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x,
+                                     void *x_ring, void *k_cache, void *v_cache, int32_t *state,
+                                     const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
+                                     int step_is_open, void *stream) {
+  return attn_step_project(q_out, wqkv, bqkv, x, x_ring, k_cache, v_cache, state, head_idx, nnz, d, nheads, hd, S, 1,
+                           step_is_open, stream);
+}
+
+extern "C" int djv_attn_step_project_batch(void *q_out, const void *wqkv, const void *bqkv, const void *x,
+                                           void *x_ring, void *k_cache, void *v_cache, int32_t *state,
+                                           const int32_t *head_idx, int nnz, int d, int nheads, int hd, int S,
+                                           int B, void *stream) {
+  return attn_step_project(q_out, wqkv, bqkv, x, x_ring, k_cache, v_cache, state, head_idx, nnz, d, nheads, hd, S, B,
+                           0, stream);
+}
+
+static int attn_step_attend(void *ctx, const void *q, const void *k_cache, const void *v_cache, int32_t *state,
+                            int B, int nheads, int hd, int S, float softmax_scale, void *scratch,
+                            size_t scratch_bytes, void *stream) {
   DJV_REQUIRE(ctx && q && k_cache && v_cache && state, "attn_step: null pointer");
   DJV_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attn_step: head_dim %d not in {32,64,128}", hd);
+  DJV_REQUIRE(B >= 1 && B <= 65535, "attn_step: batch %d outside [1,65535]", B);
   DJV_REQUIRE(nheads >= 1 && nheads <= 1024, "attn_step: nheads=%d outside [1,1024]", nheads);
   DJV_REQUIRE(S >= 1, "attn_step: cache capacity S=%d", S);
   DJV_REQUIRE(aligned16(k_cache) && aligned16(v_cache), "attn_step: pointers must be 16-byte aligned");
@@ -963,9 +1019,23 @@ extern "C" int djv_attn_step_attend(void *ctx, const void *q, const void *k_cach
   t.state = state;
   t.nnz = nheads; t.nheads = nheads; t.hd = hd; t.S = S; t.len = 0;
   t.scale = softmax_scale;
-  int rc = launch_attn(t, nheads, 1, scratch, scratch_bytes, static_cast<cudaStream_t>(stream), "attn_step");
+  int rc = launch_attn(t, nheads, B, scratch, scratch_bytes, static_cast<cudaStream_t>(stream), "attn_step");
   if (rc) return rc;
   return check_launch("attn_step_attend");
+}
+
+extern "C" int djv_attn_step_attend(void *ctx, const void *q, const void *k_cache, const void *v_cache,
+                                    int32_t *state, int nheads, int hd, int S, float softmax_scale,
+                                    void *scratch, size_t scratch_bytes, void *stream) {
+  return attn_step_attend(ctx, q, k_cache, v_cache, state, 1, nheads, hd, S, softmax_scale, scratch, scratch_bytes,
+                          stream);
+}
+
+extern "C" int djv_attn_step_attend_batch(void *ctx, const void *q, const void *k_cache, const void *v_cache,
+                                          int32_t *state, int B, int nheads, int hd, int S, float softmax_scale,
+                                          void *scratch, size_t scratch_bytes, void *stream) {
+  return attn_step_attend(ctx, q, k_cache, v_cache, state, B, nheads, hd, S, softmax_scale, scratch, scratch_bytes,
+                          stream);
 }
 
 extern "C" int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, const void *x,

@@ -58,7 +58,10 @@ MLP_IDX_JOIN = os.environ.get("DJV_MLP_IDX_JOIN", "attend")
 # the weights a rank gathers per layer stay below DJV_L2_PREFETCH_MB (development knob)
 L2_PREFETCH = os.environ.get("DJV_L2_PREFETCH", "0")
 L2_PREFETCH_MB = float(os.environ.get("DJV_L2_PREFETCH_MB", "100"))
-# batch >= 4: the per-sequence attention chains of sequences 1.. run on up to this many extra streams (branches of
+# batch > 1: the attention of all sequences runs through the batch entry points (one state, one launch per kernel
+# for the whole batch); "0": sequence by sequence through the batch-1 kernels (development knob)
+BATCHED_ATTENTION = os.environ.get("DJV_BATCHED_ATTENTION", "1") != "0"
+# sequence by sequence, batch >= 4: the attention chains of sequences 1.. run on up to this many extra streams (branches of
 # the captured graph), at least two sequences per stream, once sequence 0 has brought the selected heads' weights
 # into L2; 0 = all on the main stream. Measured on OPT-6.7B, one GPU, ms per step without / with: batch 8 7.95 /
 # 5.65, batch 16 16.9 / 8.4; one sequence per stream (batch 4 on 3 streams) was slower than none (4.9 / 4.7).
@@ -461,6 +464,24 @@ class ParallelMHASparseAttMlp(nn.Module):
             } for _ in range(batch)]}
         return self._bufs["seqs"]
 
+    def _batch_buffers(self, device, S, batch):
+        """Buffers of the batched decode step: the sequences share sequence 0's state; windows, queries and
+        contexts are contiguous over the batch."""
+        seqs = self._decode_buffers(device, S, batch)
+        bb = self._bufs.get("batch")
+        if bb is None or bb["B"] < batch:
+            n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
+            need = _lib.load().djv_decode_attn_scratch_bytes(n, batch, hd, S)
+            bb = self._bufs["batch"] = {
+                "B": batch,
+                "x_ring": torch.zeros(batch, KV_WINDOW, d, dtype=torch.float16, device=device),
+                "q": torch.zeros(batch, n, hd, dtype=torch.float16, device=device),
+                "ctx": torch.zeros(batch, n, hd, dtype=torch.float16, device=device),
+                "scratch": torch.zeros(max(need, 4096), dtype=torch.uint8, device=device),
+            }
+        bb["state"] = seqs[0]["state"]
+        return bb
+
     def reset_decode_state(self, prompt_len: int, device, S: int, batch: int = 1):
         for b in self._decode_buffers(device, S, batch):
             call("djv_attn_state_reset", b["state"].data_ptr(), self.num_head_per_node, int(prompt_len), ops._stream())
@@ -516,6 +537,28 @@ class ParallelMHASparseAttMlp(nn.Module):
         early = EARLY_PREFETCH and step_is_open == 1 and getattr(head_idx, "_ready_event", None) is not None
         out = torch.empty(B, d, dtype=x.dtype, device=x.device)
         ob = self.out_proj.bias
+        if B > 1 and BATCHED_ATTENTION and x.is_cuda:
+            # one state for the batch (shared selection, lockstep windows): one launch per kernel whatever B is
+            assert k_cache.is_contiguous() and v_cache.is_contiguous()
+            bb = self._batch_buffers(x.device, S, B)
+            state = bb["state"]
+            call("djv_attn_step_project_batch", bb["q"].data_ptr(), self.Wqkv.weight.data_ptr(),
+                 None if bias is None else bias.data_ptr(), xf.data_ptr(), bb["x_ring"].data_ptr(),
+                 k_cache.data_ptr(), v_cache.data_ptr(), state.data_ptr(),
+                 None if head_idx is None else head_idx.data_ptr(), nnz, d, n, hd, S, B, ops._stream())
+            if between is not None:
+                between()
+            call("djv_attn_step_attend_batch", bb["ctx"].data_ptr(), bb["q"].data_ptr(), k_cache.data_ptr(),
+                 v_cache.data_ptr(), state.data_ptr(), B, n, hd, S, float(self.softmax_scale),
+                 bb["scratch"].data_ptr(), bb["scratch"].numel(), ops._stream())
+            eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
+            n_eff_ptr = state.data_ptr() + 4 * 2
+            for b0 in range(0, B, 16):  # (the out_proj kernel takes up to 16 rows per launch)
+                nb = min(16, B - b0)
+                call("djv_out_proj_sparse", out[b0].data_ptr(), self.out_proj.weight.data_ptr(),
+                     bb["ctx"][b0].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), nb, d,
+                     n, hd, n, ops._stream())
+            return out.view(B, 1, d)
 
         def project(i, b):
             call("djv_attn_step_project", b["q"].data_ptr(), self.Wqkv.weight.data_ptr(),

@@ -258,6 +258,18 @@ int djv_attn_step(void *ctx, void *q_out, const void *wqkv, const void *bqkv, co
 int djv_attn_step_project(void *q_out, const void *wqkv, const void *bqkv, const void *x, void *x_ring,
                           void *k_cache, void *v_cache, int32_t *state, const int32_t *head_idx, int nnz,
                           int d, int nheads, int hd, int S, int step_is_open, void *stream);
+/* The same two calls for B sequences that decode in lockstep and share ONE state: one head selection per layer
+ * and step (the reference's decode path keeps one sequence, mha_dejavu.py:1318, 1469; its kernels take one index
+ * list for all rows of a batch) and therefore one window position and one set of pending rows. Per-sequence data is
+ * contiguous over the batch: q_out / q / ctx (B,nheads,hd), x (B,d), x_ring (B,16,d), k_cache (B,nheads,hd/8,S,8),
+ * v_cache (B,nheads,S,hd); scratch >= djv_decode_attn_scratch_bytes(nheads, B, hd, S). One launch each whatever B
+ * is: the blocks of all sequences that work on the same weight rows run side by side and share them through L2. */
+int djv_attn_step_project_batch(void *q_out, const void *wqkv, const void *bqkv, const void *x, void *x_ring,
+                                void *k_cache, void *v_cache, int32_t *state, const int32_t *head_idx, int nnz,
+                                int d, int nheads, int hd, int S, int B, void *stream);
+int djv_attn_step_attend_batch(void *ctx, const void *q, const void *k_cache, const void *v_cache, int32_t *state,
+                               int B, int nheads, int hd, int S, float softmax_scale, void *scratch,
+                               size_t scratch_bytes, void *stream);
 /* Top-K of the head predictor's scores (one score per head of this rank) that also opens the decode step
  * of the attention layer the selection is for: djv_topk(idx32, ...) followed by the head-selection half of
  * step 1 above on `state`, in one launch, off the critical path (mha_dejavu.py:1364-1370 computes the

@@ -140,13 +140,20 @@ def test_decode_matches_oracle_at_real_widths(cuda, d, heads, mlp_K, att_K, step
     assert all(m.mixer.decode_status() == 0 for m in model.transformer.layers)
 
 
-@pytest.mark.parametrize("B,mlp_K,att_K,local_exchange", [(3, 256, 2, False), (4, 256, 2, True), (2, 1024, 4, False),
-                                                         (5, 256, 2, True)])
-def test_batched_decode_shares_one_index_set_and_matches_oracle(cuda, B, mlp_K, att_K, local_exchange):
+@pytest.mark.parametrize("B,mlp_K,att_K,local_exchange,batched", [
+    (3, 256, 2, False, True), (4, 256, 2, True, True), (2, 1024, 4, False, True), (5, 256, 2, True, True),
+    (18, 256, 2, False, True),   # more rows than one out_proj launch takes
+    (5, 256, 2, False, False),   # sequence by sequence, two extra streams
+    (9, 1024, 4, False, False)])
+def test_batched_decode_shares_one_index_set_and_matches_oracle(cuda, monkeypatch, B, mlp_K, att_K, local_exchange,
+                                                                batched):
     """Several sequences decode in lockstep with ONE index set per layer and step (top-K of the predictor logits
-    summed over the batch); every sequence's logits follow the oracle, which applies the same rule."""
+    summed over the batch); every sequence's logits follow the oracle, which applies the same rule. `batched`: the
+    attention of the whole batch through the batch entry points (one state), else through the batch-1 kernels."""
+    from dejavu_b200 import modules
     from dejavu_b200.generation import InferenceParams, allocate_kv_cache
 
+    monkeypatch.setattr(modules, "BATCHED_ATTENTION", batched)
     cfg = tiny_config(mlp_K, att_K, n_layer=3)
     model = build(cfg, cuda, local_exchange=False)
     if local_exchange:
