@@ -31,9 +31,10 @@ int check_launch(const char *what) {
 static thread_local int g_early_prefetch = 0;
 bool early_prefetch() { return g_early_prefetch != 0 && pdl_enabled(); }
 
+static thread_local int g_programmatic_launch = 1;
 bool pdl_enabled() {
   static const bool on = env_int("DJV_PDL", 1) != 0;
-  return on;
+  return on && g_programmatic_launch != 0;
 }
 
 int sm_count() {
@@ -54,6 +55,8 @@ int sm_count() {
 extern "C" int djv_version(void) { return 100; }
 
 extern "C" void djv_set_early_weight_prefetch(int enabled) { djv::g_early_prefetch = enabled; }
+
+extern "C" void djv_set_programmatic_launch(int enabled) { djv::g_programmatic_launch = enabled; }
 
 extern "C" const char *djv_last_error(void) { return djv::g_err; }
 

@@ -307,9 +307,10 @@ extern "C" int djv_gather_gemv(void *y, const void *w, const void *x, const void
 extern "C" size_t djv_gather_transposed_gemv_scratch_bytes(int B, int N, int M) {
   if (B < 1 || N < 8 || M < 0) return 0;
   if (B > RA_MAX_B) return rowaxpy_mma_scratch_bytes(B, N, M > 0 ? M : 1);  // tensor-core kernel, one pass
-  // a call is cut into slices of up to 4 rows of x, and the plan depends on the slice's row count
+  // up to 4 rows of x: the CUDA-core kernel's plan depends on the row count (and djv_gather_transposed_gemv_push
+  // always runs it); 3 and 4 rows otherwise go to the tensor-core kernel
   const int bs = B < 4 ? B : 4;
-  size_t need = 0;
+  size_t need = B >= RA_MMA_MIN_B ? rowaxpy_mma_scratch_bytes(B, N, M > 0 ? M : 1) : 0;
   for (int b = 1; b <= bs; ++b) {
     const size_t n = rowaxpy_scratch_bytes(b, N, M);
     if (n > need) need = n;
@@ -344,7 +345,7 @@ extern "C" int djv_gather_transposed_gemv(void *y, const void *w, const void *x,
     if (rc) return rc;
     return check_launch("gather_transposed_gemv");
   }
-  if (B > RA_MAX_B) {  // 5..32 activation rows: tensor cores, every gathered row read once
+  if (B >= RA_MMA_MIN_B) {  // 3..32 activation rows: tensor cores, every gathered row read once
     rc = rowaxpy_mma(B, static_cast<__half *>(y), static_cast<const __half *>(w), static_cast<const __half *>(x), idx,
                      static_cast<const __half *>(bias), scratch, M, N, ldw, idx_is_64, st);
     if (rc) return rc;

@@ -25,6 +25,7 @@ constexpr int RA_CLUSTER = 8;
 constexpr int RA_MAX_MCC = 6;
 constexpr int RA_COUNTER_BYTES = 4096;
 constexpr int RA_MAX_B = 4;
+constexpr int RA_MMA_MIN_B = 3;  // djv_gather_transposed_gemv: from this many rows of x on, the tensor-core kernel
 
 // Last stage of rowaxpy_kernel:
 // the block adds the 8 blocks' sums for its slice of columns and either stores them (one cluster per column

@@ -206,38 +206,51 @@ rowaxpy_mma_kernel(__half *__restrict__ Y, const __half *__restrict__ W, const _
       }
 }
 
-// y[b, n] = sum over the row blocks of partial[k][b][n] + bias[n], in block order (deterministic); a thread takes 8
-// consecutive columns and requests all blocks' sums (up to 8 at a time) before it adds them.
-__global__ void __launch_bounds__(256)
+// y[b, n] = sum over the row blocks of partial[k][b][n] + bias[n] (deterministic). A block takes 256 columns of one
+// activation row: lane l of every warp owns 8 of them, warp w adds the row blocks w, w + 8, ... in order (up to 4
+// requested at a time), then the 8 warps' sums are added in warp order through shared memory.
+constexpr int RM_RED_WARPS = 8;
+__global__ void __launch_bounds__(RM_RED_WARPS * WARP)
 rowaxpy_mma_reduce_kernel(__half *__restrict__ Y, const float *__restrict__ partial, const __half *__restrict__ bias,
                           int B, int N, int RS) {
   pdl_prologue();
-  const int chunks = N / 8;
-  const int o = blockIdx.x * blockDim.x + threadIdx.x;
-  if (o >= B * chunks) return;
-  const int b = o / chunks, n = (o % chunks) * 8;
+  __shared__ float red[RM_RED_WARPS][WARP][8];
+  const int lane = threadIdx.x % WARP, warp = threadIdx.x / WARP;
+  const int b = blockIdx.y, n = (blockIdx.x * WARP + lane) * 8;
+  const bool inside = n < N;  // N % 8 == 0
   float v[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) v[e] = 0.f;
-  for (int k0 = 0; k0 < RS; k0 += 8) {
-    float4 lo[8], hi[8];
+  if (inside) {
+    for (int k0 = warp; k0 < RS; k0 += RM_RED_WARPS * 4) {
+      float4 lo[4], hi[4];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (k0 + u < RS) {
-        const float4 *src = reinterpret_cast<const float4 *>(partial + ((size_t)(k0 + u) * B + b) * N + n);
-        lo[u] = __ldcg(src);
-        hi[u] = __ldcg(src + 1);
-      } else {
-        lo[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        hi[u] = lo[u];
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + u * RM_RED_WARPS;
+        if (k < RS) {
+          const float4 *src = reinterpret_cast<const float4 *>(partial + ((size_t)k * B + b) * N + n);
+          lo[u] = __ldcg(src);
+          hi[u] = __ldcg(src + 1);
+        } else {
+          lo[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          hi[u] = lo[u];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[0] += lo[u].x; v[1] += lo[u].y; v[2] += lo[u].z; v[3] += lo[u].w;
+        v[4] += hi[u].x; v[5] += hi[u].y; v[6] += hi[u].z; v[7] += hi[u].w;
       }
     }
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      v[0] += lo[u].x; v[1] += lo[u].y; v[2] += lo[u].z; v[3] += lo[u].w;
-      v[4] += hi[u].x; v[5] += hi[u].y; v[6] += hi[u].z; v[7] += hi[u].w;
-    }
   }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[warp][lane][e] = v[e];
+  __syncthreads();
+  if (warp != 0 || !inside) return;
+#pragma unroll
+  for (int w = 1; w < RM_RED_WARPS; ++w)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] += red[w][lane][e];
   if (bias != nullptr) {
     const uint4 bv = ld_cached16(bias + n);
     const float2 b0 = h2f(bv.x), b1 = h2f(bv.y), b2 = h2f(bv.z), b3 = h2f(bv.w);
@@ -274,7 +287,7 @@ inline size_t rowaxpy_mma_scratch_bytes(int B, int N, int M) {
   return 4096 + (p.rs > 1 ? (size_t)p.rs * B * N * sizeof(float) : 0);
 }
 
-// 5 <= B <= 32
+// 1 <= B <= 32 (used from 3 rows up)
 inline int rowaxpy_mma(int B, __half *Y, const __half *W, const __half *X, const void *idx, const __half *bias,
                        void *scratch, int M, int N, long long ldw, int idx64, cudaStream_t st) {
   const RowaxpyMmaPlan p = plan_rowaxpy_mma(M, N);
@@ -299,7 +312,7 @@ inline int rowaxpy_mma(int B, __half *Y, const __half *W, const __half *X, const
                        partial, M, N, ldw, idx64, B, p.rows_per_block);
   count_launch();
   if (p.rs > 1) {
-    djv::launch_kernel(rowaxpy_mma_reduce_kernel, dim3(ceil_div(B * (N / 8), 256)), dim3(256), 0, st, Y,
+    djv::launch_kernel(rowaxpy_mma_reduce_kernel, dim3(ceil_div(N / 8, WARP), B), dim3(RM_RED_WARPS * WARP), 0, st, Y,
                        static_cast<const float *>(partial), bias, B, N, p.rs);
     count_launch();
   }

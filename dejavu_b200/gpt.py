@@ -19,7 +19,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import ops
+from . import _lib, modules, ops
 from .generation import GenerationMixin
 from .modules import (BlockDejavu, BlockMlpAttSparse, ColumnParallelLinear, ParallelFusedMLP,
                       ParallelFusedMLPDejavu, ParallelMHADejavu, ParallelMHASparseAttMlp, _rank, _world,
@@ -230,6 +230,19 @@ class GPTLMHeadModel(nn.Module, GenerationMixin):
         self.lm_head.weight = self.transformer.embeddings.word_embeddings.weight
 
     def forward(self, input_ids, position_ids=None, inference_params=None):
+        # A decode step of several sequences runs kernels of several waves of blocks: programmatic dependent launch
+        # then costs more than it hides (see djv_set_programmatic_launch), so the step's kernels are launched plain.
+        plain = (input_ids.is_cuda and input_ids.size(0) > 1 and input_ids.size(1) == 1
+                 and not modules.BATCH_PROGRAMMATIC_LAUNCH)
+        if plain:
+            _lib.load().djv_set_programmatic_launch(0)
+        try:
+            return self._forward(input_ids, position_ids, inference_params)
+        finally:
+            if plain:
+                _lib.load().djv_set_programmatic_launch(1)
+
+    def _forward(self, input_ids, position_ids=None, inference_params=None):
         hidden_states = self.transformer(input_ids, position_ids=position_ids, inference_params=inference_params)
         B, L, d = hidden_states.shape
         if L == 1 and hidden_states.is_cuda and B <= 32:

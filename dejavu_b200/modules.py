@@ -58,6 +58,9 @@ MLP_IDX_JOIN = os.environ.get("DJV_MLP_IDX_JOIN", "attend")
 # the weights a rank gathers per layer stay below DJV_L2_PREFETCH_MB (development knob)
 L2_PREFETCH = os.environ.get("DJV_L2_PREFETCH", "0")
 L2_PREFETCH_MB = float(os.environ.get("DJV_L2_PREFETCH_MB", "100"))
+# batch > 1: keep programmatic dependent launch for the decode step's kernels ("1"); default off, measured slower
+# (OPT-6.7B, 16 sequences: 6.3 ms per step with, 4.7 without; 4 sequences: 2.95 / 2.64) (development knob)
+BATCH_PROGRAMMATIC_LAUNCH = os.environ.get("DJV_BATCH_PDL", "0") != "0"
 # batch > 1: the attention of all sequences runs through the batch entry points (one state, one launch per kernel
 # for the whole batch); "0": sequence by sequence through the batch-1 kernels (development knob)
 BATCHED_ATTENTION = os.environ.get("DJV_BATCHED_ATTENTION", "1") != "0"

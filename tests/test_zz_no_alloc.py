@@ -43,8 +43,11 @@ def _static(lib_mod, W, h, bias, idx, B, N, M):
     return y
 
 
-@pytest.mark.parametrize("Z,N,M,B", [(6144, 12288, 512, 1), (2048, 4096, 700, 3)])
+@pytest.mark.parametrize("Z,N,M,B", [(6144, 12288, 512, 1), (2048, 4096, 700, 2), (2048, 4096, 700, 3),
+                                     (8192, 2048, 4096, 4)])
 def test_static_scratch_entry_point_matches_regular_one_twice(cuda, Z, N, M, B):
+    """Up to 2 rows of x both entry points run the same kernel with the same plan: identical bits. With 3 and 4 rows
+    the regular entry point uses the tensor-core kernel (another summation order): equal within the tolerance."""
     from dejavu_b200 import _lib
 
     for call_no, seed in enumerate((21, 22)):  # two calls in a row: the array keeps the first call's leftovers
@@ -54,10 +57,11 @@ def test_static_scratch_entry_point_matches_regular_one_twice(cuda, Z, N, M, B):
         torch.cuda.synchronize()
         # same kernel, same plan, same summation order: the tolerance of the other tests is met exactly
         assert torch.allclose(got.float(), want.float(), atol=1e-3, rtol=1e-2), f"call {call_no}"
-        assert torch.equal(got, want), f"call {call_no}: expected identical bits"
+        if B <= 2:
+            assert torch.equal(got, want), f"call {call_no}: expected identical bits"
 
 
-@pytest.mark.parametrize("Z,M,B,widths", [(8192, 4096, 1, (1024, 2048)), (8192, 4096, 4, (2048, 1024))])
+@pytest.mark.parametrize("Z,M,B,widths", [(8192, 4096, 1, (1024, 2048)), (8192, 4096, 2, (2048, 1024))])
 def test_static_scratch_array_is_really_used_and_reused(cuda, Z, M, B, widths):
     """Shapes whose plan splits the index list over several clusters per column tile: the kernel then keeps
     per-cluster partial sums and arrival counters in the built-in array. Two calls in a row with DIFFERENT
