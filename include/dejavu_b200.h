@@ -99,8 +99,8 @@ int djv_gather_gemv(void *y, const void *w, const void *x, const void *idx, cons
  * Gather transposed GEMV (fc2):  y[b,n] = sum_m w[idx[m],n] * x[b,m] + bias[n].
  * Replaces gather_transposed_gemv, Dejavu/src/ops/triton/gather_gemv.py:572-644 (both its
  * atomic-add and its deterministic kernel, :432-569 and :263-425). Deterministic: partial sums over
- * fixed row chunks are written to scratch and combined in a fixed order (B <= 4: by the last block to finish;
- * 5 <= B <= 32: tensor-core kernel, one pass over the gathered rows whatever B is, then a small second kernel
+ * fixed row chunks are written to scratch and combined in a fixed order (B <= 2: by the last block to finish;
+ * 3 <= B <= 32: tensor-core kernel, one pass over the gathered rows whatever B is, then a small second kernel
  * that adds the row chunks).
  *   y (B,N) fp16 | w (Z,N) stride ldw = W2 transposed | x (B,M) | idx (M,) or NULL | bias (N,) or NULL.
  *   scratch: at least djv_gather_transposed_gemv_scratch_bytes(B,N,M) bytes, 256-byte aligned, and its
