@@ -92,6 +92,9 @@ GATHER_CASES = [
     (6144, 1024, 4805, 20, "rand64"),  # ragged last tile; activations not 16-byte aligned per row
     (2048, 1000, 304, 24, "sorted32"), # last column tile partly outside the rows
     (8192, 512, 2500, 5, "dup64"),
+    (12000, 1000, 10000, 16, "rand32"),  # short rows, long list: a 16-row tile per warp
+    (16384, 1000, 16384, 9, "none"),     # the predictor's second layer for a batch
+    (10000, 264, 9999, 32, "rand64"),
 ]
 
 
