@@ -518,9 +518,11 @@ class ParallelMHASparseAttMlp(nn.Module):
     def _decode_attention(self, x, head_idx, inference_params, between=None):
         """One decode step of this layer's attention; `between()` is called after the projection kernels are
         queued and before the attention kernel (the place to fork look-ahead work onto a side stream).
-        A batch runs sequence by sequence through the same kernels (each sequence has its own window and caches;
-        the head selection is shared): sequence 0 on the main stream, the others, whose weights then come from L2,
-        as parallel chains on up to BATCH_STREAMS extra streams that rejoin before the result is used."""
+        A batch shares the head selection and advances in lockstep, so its sequences have identical windows: it
+        runs through the batch entry points with one state (one launch per kernel). With BATCHED_ATTENTION off it
+        runs sequence by sequence through the batch-1 kernels: sequence 0 on the main stream, the others, whose
+        weights then come from L2, as parallel chains on up to BATCH_STREAMS extra streams that rejoin before the
+        result is used."""
         n, hd, d = self.num_head_per_node, self.head_dim, self.embed_dim
         B = x.size(0)
         k_cache, v_cache = inference_params.key_value_memory_dict[self.layer_idx]
