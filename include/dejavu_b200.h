@@ -64,9 +64,11 @@ void djv_set_early_weight_prefetch(int enabled);
 /* Per calling thread, default 1. Every kernel of the library is launched with programmatic dependent launch and
  * lets its successor start (and wait) as soon as all its own blocks have started: the successor's launch latency
  * and prologue overlap the kernel's tail. That pays when kernels are short and fit the device in one wave (decode
- * with one sequence); when a kernel runs several waves of blocks, the waiting blocks of its successor take the
- * multiprocessor slots its own later blocks need (measured: OPT-6.7B, 16 sequences, 6.3 ms per step with, 4.7
- * without). 0 launches the kernels of this thread as plain stream-ordered kernels. Never changes a result. */
+ * with one sequence: OPT-66B 7.18 ms per token with it, 7.4 without). In decode steps of several sequences it was
+ * measured to cost far more than it hides (OPT-6.7B, ms per step with / without: 2 sequences 4.58 / 2.37, 16
+ * sequences 6.3 / 4.7); the likely cause: the waiting blocks of a successor hold multiprocessor slots that the later
+ * blocks of a kernel of several waves need. 0 launches the kernels of this thread as plain stream-ordered kernels.
+ * Never changes a result. */
 void djv_set_programmatic_launch(int enabled);
 
 /* ---------------------------------------------------------------------------------------------
