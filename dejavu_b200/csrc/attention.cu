@@ -807,6 +807,7 @@ static int launch_out_proj(int B, __half *Y, const __half *W, const __half *X, c
     case 2: DJV_OP(2); break;
     case 3: DJV_OP(3); break;
     case 4: DJV_OP(4); break;
+    case 8: DJV_OP(8); break;
     default: set_error("out_proj_sparse: internal batch slice %d", B); return DJV_ERR_INVALID;
   }
 #undef DJV_OP
@@ -823,8 +824,9 @@ extern "C" int djv_out_proj_sparse(void *y, const void *w, const void *x, const 
   DJV_REQUIRE(nnz >= 0 && nnz <= nheads, "out_proj_sparse: nnz=%d outside [0,%d]", nnz, nheads);
   DJV_REQUIRE(aligned16(w) && aligned16(x), "out_proj_sparse: w and x must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  for (int b0 = 0; b0 < B; b0 += 4) {
-    const int bs = (B - b0 < 4) ? (B - b0) : 4;
+  // slices of 8 rows of x while 8 are left, then of up to 4 (each slice reads the selected columns once)
+  for (int b0 = 0, bs = 0; b0 < B; b0 += bs) {
+    bs = (B - b0 >= 8) ? 8 : ((B - b0 < 4) ? (B - b0) : 4);
     __half *Y = static_cast<__half *>(y) + (size_t)b0 * d;
     const __half *X = static_cast<const __half *>(x) + (size_t)b0 * nheads * hd;
     const __half *W = static_cast<const __half *>(w);
