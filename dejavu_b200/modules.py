@@ -58,6 +58,9 @@ MLP_IDX_JOIN = os.environ.get("DJV_MLP_IDX_JOIN", "attend")
 # the weights a rank gathers per layer stay below DJV_L2_PREFETCH_MB (development knob)
 L2_PREFETCH = os.environ.get("DJV_L2_PREFETCH", "0")
 L2_PREFETCH_MB = float(os.environ.get("DJV_L2_PREFETCH_MB", "100"))
+# batch > 1: the predictors run once, on the sum of the sequences' inputs (they are linear), instead of once per
+# sequence; "0": per sequence, logits added afterwards (development knob)
+SP_SUM_INPUTS = os.environ.get("DJV_SP_SUM_INPUTS", "1") != "0"
 # batch > 1: keep programmatic dependent launch for the decode step's kernels ("1"); default off, measured slower
 # (OPT-6.7B, 16 sequences: 6.3 ms per step with, 4.7 without; 4 sequences: 2.95 / 2.64) (development knob)
 BATCH_PROGRAMMATIC_LAUNCH = os.environ.get("DJV_BATCH_PDL", "0") != "0"
@@ -254,11 +257,16 @@ class ParallelSP(nn.Module):
         self.K = K // _world(process_group)
 
     def forward(self, x):
-        """x (1, 1, d) -> logits (out,). A batch (B, 1, d) gives ONE score vector: the sum of the sequences' logits
-        (fp32 sum of the fp16 logits, rounded to fp16), so that the whole batch shares one index set per step, as
-        the reference's kernels expect (one idx for all rows, Dejavu/src/ops/triton/gather_gemv.py:198-254); its
-        decode path itself keeps a single sequence (mha_dejavu.py:1318, 1469)."""
-        x = ops.dense_gemv(x.reshape(-1, self.embed_dim), self.fc0.weight)  # B x low_rank
+        """x (1, 1, d) -> logits (out,). A batch (B, 1, d) gives ONE score vector: the sum of the sequences' logits,
+        so that the whole batch shares one index set per step, as the reference's kernels expect (one idx for all
+        rows, Dejavu/src/ops/triton/gather_gemv.py:198-254); its decode path itself keeps a single sequence
+        (mha_dejavu.py:1318, 1469). Both layers are linear and bias-free, so the sum of the logits is the predictor
+        applied to the sum of the inputs: the batch costs the two GEMVs of ONE sequence (SP_SUM_INPUTS; with it
+        off, every sequence's logits are computed and added in fp32). The two forms differ by fp16 rounding only."""
+        x = x.reshape(-1, self.embed_dim)
+        if x.size(0) > 1 and SP_SUM_INPUTS:
+            x = x.float().sum(0, keepdim=True).to(x.dtype)
+        x = ops.dense_gemv(x, self.fc0.weight)  # B x low_rank
         x = ops.dense_gemv(x, self.fc1.weight)
         if x.size(0) == 1:
             return x.view(-1)
