@@ -566,7 +566,7 @@ class ParallelMHASparseAttMlp(nn.Module):
                  bb["scratch"].data_ptr(), bb["scratch"].numel(), ops._stream())
             eff_heads_ptr = state.data_ptr() + 4 * (_lib.ATTN_STATE_HDR + n)
             n_eff_ptr = state.data_ptr() + 4 * 2
-            for b0 in range(0, B, 16):  # (the out_proj kernel takes up to 16 rows per launch)
+            for b0 in range(0, B, 16):  # (djv_out_proj_sparse takes up to 16 rows per call)
                 nb = min(16, B - b0)
                 call("djv_out_proj_sparse", out[b0].data_ptr(), self.out_proj.weight.data_ptr(),
                      bb["ctx"][b0].data_ptr(), eff_heads_ptr, n_eff_ptr, None if ob is None else ob.data_ptr(), nb, d,
