@@ -66,9 +66,10 @@ void djv_set_early_weight_prefetch(int enabled);
  * and prologue overlap the kernel's tail. That pays when kernels are short and fit the device in one wave (decode
  * with one sequence: OPT-66B 7.18 ms per token with it, 7.4 without). In decode steps of several sequences it was
  * measured to cost far more than it hides (OPT-6.7B, ms per step with / without: 2 sequences 4.58 / 2.37, 16
- * sequences 6.3 / 4.7); the likely cause: the waiting blocks of a successor hold multiprocessor slots that the later
- * blocks of a kernel of several waves need. 0 launches the kernels of this thread as plain stream-ordered kernels.
- * Never changes a result. */
+ * sequences 6.3 / 4.7). The step timeline shows why: successors launched early sit on the multiprocessors waiting,
+ * and a kernel of another stream that they depend on through an event (in the batched step: the host framework's
+ * own reduction kernels of the look-ahead predictor) finds no free slot for some 200 us per layer. 0 launches the
+ * kernels of this thread as plain stream-ordered kernels. Never changes a result. */
 void djv_set_programmatic_launch(int enabled);
 
 /* ---------------------------------------------------------------------------------------------
