@@ -79,6 +79,7 @@ SIGNATURES = {
                                            _i, _i, _i, _i, _ll, _ll, _i, _vp, _sz, _vp]),
     "djv_set_early_weight_prefetch": (None, [_i]),
     "djv_set_programmatic_launch": (None, [_i]),
+    "djv_batch_sum": (_i, [_vp, _vp, _i, _i, _vp]),
     "djv_comm_destroy": (_i, [_vp]),
     "djv_comm_status": (_i, [_vp]),
     "djv_allreduce_add_layernorm": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),

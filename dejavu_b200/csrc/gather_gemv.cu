@@ -248,9 +248,28 @@ __global__ void bias_fill_kernel(__half *Y, const __half *bias, int B, int N) {
   if (i < B * N) Y[i] = bias ? bias[i % N] : __float2half(0.f);
 }
 
+// y[n] = sum over b of x[b, n], added in fp32 in row order, rounded once
+__global__ void batch_sum_kernel(__half *__restrict__ Y, const __half *__restrict__ X, int B, int N) {
+  pdl_prologue();
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float s = 0.f;
+  for (int b = 0; b < B; ++b) s += __half2float(X[(size_t)b * N + n]);
+  Y[n] = __float2half_rn(s);
+}
+
 }  // namespace djv
 
 using namespace djv;
+
+extern "C" int djv_batch_sum(void *y, const void *x, int B, int N, void *stream) {
+  DJV_REQUIRE(y && x, "batch_sum: null pointer");
+  DJV_REQUIRE(B >= 1 && N >= 1, "batch_sum: B=%d N=%d", B, N);
+  djv::launch_kernel(batch_sum_kernel, ceil_div(N, 256), 256, 0, static_cast<cudaStream_t>(stream),
+                     static_cast<__half *>(y), static_cast<const __half *>(x), B, N);
+  count_launch();
+  return check_launch("batch_sum");
+}
 
 static int check_common(const char *op, const void *y, const void *w, const void *x, int B, int N,
                         int M, long long ldw) {

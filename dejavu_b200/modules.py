@@ -264,13 +264,18 @@ class ParallelSP(nn.Module):
         applied to the sum of the inputs: the batch costs the two GEMVs of ONE sequence (SP_SUM_INPUTS; with it
         off, every sequence's logits are computed and added in fp32). The two forms differ by fp16 rounding only."""
         x = x.reshape(-1, self.embed_dim)
+        def rows_sum(t):  # fp32 sum of the rows, rounded once
+            if t.is_cuda and t.dtype == torch.float16:
+                return ops.batch_sum(t)
+            return t.float().sum(0, keepdim=True).to(t.dtype)
+
         if x.size(0) > 1 and SP_SUM_INPUTS:
-            x = x.float().sum(0, keepdim=True).to(x.dtype)
+            x = rows_sum(x)
         x = ops.dense_gemv(x, self.fc0.weight)  # B x low_rank
         x = ops.dense_gemv(x, self.fc1.weight)
-        if x.size(0) == 1:
-            return x.view(-1)
-        return x.float().sum(0).to(x.dtype)
+        if x.size(0) > 1:
+            x = rows_sum(x)
+        return x.view(-1)
 
 
 class ParallelFusedMLPDejavu(nn.Module):

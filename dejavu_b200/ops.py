@@ -394,6 +394,15 @@ def topk_indices(scores: torch.Tensor, k: int, dtype: torch.dtype = torch.int64)
     return out
 
 
+def batch_sum(x: torch.Tensor) -> torch.Tensor:
+    """(B, N) fp16 -> (1, N): the rows added in fp32, rounded once (djv_batch_sum)."""
+    assert x.is_cuda and x.dtype == torch.float16 and x.dim() == 2
+    x = x.contiguous()
+    y = torch.empty(1, x.size(1), dtype=x.dtype, device=x.device)
+    call("djv_batch_sum", y.data_ptr(), x.data_ptr(), x.size(0), x.size(1), _stream())
+    return y
+
+
 @contextlib.contextmanager
 def indices_ready(ready: bool = True):
     """Inside this block the caller promises that the index lists / attention state passed to the operators

@@ -171,6 +171,11 @@ int djv_mlp_sparse_fused(void *y, const void *w1, const void *w2t, const void *x
                          const void *bias1, const void *bias2, int B, int N, int M, int Z, long long ldw1,
                          long long ldw2t, int idx_is_64, void *scratch, size_t scratch_bytes, void *stream);
 
+/* y[n] = sum_b x[b,n] for x (B,N) fp16, added in fp32 in row order and rounded once: the batch sum in front of
+ * (or behind) the linear sparsity predictors when several sequences share one index set. No reference counterpart
+ * (its decode path keeps one sequence, mha_dejavu.py:1318, 1469). */
+int djv_batch_sum(void *y, const void *x, int B, int N, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Top-K index selection over one score vector.
  * Replaces mlp_sp_logit.topk(K, sorted=False) / att_sp_logit.topk(K) + .to(int32),

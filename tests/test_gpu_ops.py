@@ -210,6 +210,20 @@ def test_full_size_properties_175b_shard(cuda):
     close(y2, 2 * y1, atol=2e-3)
 
 
+@pytest.mark.parametrize("B,N", [(2, 4096), (5, 1000), (32, 36864), (1, 7)])
+def test_batch_sum_adds_rows_in_fp32_in_order(cuda, B, N):
+    from dejavu_b200 import ops
+
+    gen = torch.Generator().manual_seed(B * N)
+    x = rand(gen, (B, N))
+    acc = torch.zeros(N, dtype=torch.float32)
+    for b in range(B):
+        acc += x[b].float()
+    got = ops.batch_sum(x.to(cuda))
+    assert got.shape == (1, N)
+    assert torch.equal(got[0].cpu(), acc.half())
+
+
 def test_outputs_stay_inside_their_buffers(cuda):
     """Canary words around y: the kernels must not write outside (B,M) / (B,N)."""
     from dejavu_b200 import _lib
